@@ -1,0 +1,162 @@
+/* C ABI of libmok_b200: the B200 (sm_100a) implementation of the Mixture-of-Kittens MoE
+ * hot path (schedule -> dispatch -> grouped SwiGLU expert FFN -> combine, forward and
+ * backward).  Plain pointers and sizes only; no torch or C++ types cross this boundary.
+ *
+ * Conventions
+ *  - Every entry point launches on `stream` (a cudaStream_t passed as void*) and returns
+ *    immediately: 0 on success, a negative MOK_ERR_* for errors the host can detect.
+ *  - Errors only the device can detect (schedule overflow, a wait that ran out) are written
+ *    to the caller's status word: int32[4] in device memory = {code, detail, block, 0},
+ *    first error wins.  The library never traps and never waits without a limit.
+ *  - The library allocates no device memory.  Callers own inputs, outputs and scratch.
+ *  - "Reference" citations give the file:line of the interface in the Mixture-of-Kittens
+ *    project that the entry point stands in for.
+ */
+#ifndef MOK_B200_H_
+#define MOK_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MOK_MAX_PEERS 8          /* expert-parallel ranks on one NVSwitch box */
+#define MOK_MAX_LOCAL_EXPERTS 1024
+
+/* host-detected errors (return values) */
+#define MOK_OK 0
+#define MOK_ERR_INVALID (-1)     /* argument outside the documented domain */
+#define MOK_ERR_CUDA (-2)        /* a CUDA runtime / driver call failed */
+#define MOK_ERR_UNSUPPORTED (-3) /* shape or mode this build does not implement */
+
+/* device-detected errors (status word code) */
+#define MOK_STATUS_OK 0
+#define MOK_STATUS_SCHEDULE_OVERFLOW 1 /* padded routes exceed schedule_capacity; detail = needed rows */
+#define MOK_STATUS_BARRIER_TIMEOUT 2   /* a peer never arrived at mok_barrier_all; detail = counter seen */
+#define MOK_STATUS_PIPELINE_TIMEOUT 3  /* an in-kernel producer/consumer wait ran out; detail = role */
+
+int mok_version(void);
+const char* mok_error_string(int code);
+
+/* All-gather of the int32 top-k expert ids: rank `rank` stores its `numel` ids into slot `rank`
+ * of every peer's [ep_size, numel] buffer with plain peer stores over NVLink.
+ * Reference: mok/ops.py:6-58 (all_gather_top_experts), csrc/utils.cuh:230-263. */
+int mok_all_gather_top_experts(const int32_t* top_experts, int64_t numel,
+                               const uint64_t* peer_buffer_ptrs, int ep_size, int rank, void* stream);
+
+/* Device-side barrier over the expert-parallel ranks: target += ep_size, every rank adds 1 to
+ * each peer's counter, then waits (bounded by `timeout_ns`, 0 = default) until its own counter
+ * reaches the target.  On expiry the status word gets MOK_STATUS_BARRIER_TIMEOUT.
+ * Reference: mok/ops.py:61-100 (barrier_all), csrc/utils.cuh:283-313. */
+int mok_barrier_all(uint32_t* local_counter, const uint64_t* peer_counter_ptrs, int ep_size,
+                    uint32_t* target, int32_t* status, uint64_t timeout_ns, void* stream);
+
+/* Slot tables of this rank from the gathered top-k ids.  Bit-exact with the reference:
+ * thread-major route order over 1024 virtual threads, round-robin interleave of peers, each
+ * expert padded to 256 rows; unwritten slots hold -1 in both tables.
+ * `scratch` must hold mok_schedule_scratch_bytes() bytes; contents need no initialisation.
+ * Reference: mok/ops.py:103-150 (schedule), csrc/scheduler.cuh:35-183. */
+size_t mok_schedule_scratch_bytes(int ep_size, int num_local_experts);
+int mok_schedule(const int32_t* topk_all, int ep_size, int num_local_tokens, int topk,
+                 int num_local_experts, int schedule_capacity, int rank,
+                 int32_t* schedule_peer_rank, int32_t* schedule_peer_token_idx,
+                 int32_t* num_tokens, int32_t* tokens_per_expert,
+                 void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+
+/* BF16 [E, M, N] -> MXFP8: E4M3 bytes plus one E8M0 scale per 1x32 block along the last
+ * dimension, normal and/or transposed; scales in the [rows/128, cols/128, 32, 16] tcgen05
+ * block-scale layout.  Pass NULL for a layout that is not wanted.
+ * Reference: mok/ops.py:153-191 (mxfp8_quantize), csrc/mxfp8.cuh:45-72,184-278. */
+int mok_mxfp8_quantize(const void* x_bf16, int num_matrices, int rows, int cols,
+                       void* x_fp8, void* x_sc, void* x_fp8_t, void* x_sc_t, void* stream);
+
+/* out[t] = bf16(y_shared[t] + sum_k w[t,k] * combine[t*K+k]) in fp32, k ascending.
+ * Reference: mok/ops.py:1011-1045 (fwd_epilogue), csrc/utils.cuh:65-133. */
+int mok_fwd_epilogue(const void* y_shared, const void* combine_buffer, const float* topk_weights,
+                     void* output, int num_local_tokens, int hidden, int topk, void* stream);
+
+/* d_x[t] = bf16(d_x_shared[t] + sum_k d_x_routed_buffer[t*K+k]) in fp32, k ascending.
+ * Reference: mok/ops.py:1048-1081 (bwd_epilogue), csrc/utils.cuh:158-205. */
+int mok_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* d_x,
+                     int num_local_tokens, int hidden, int topk, void* stream);
+
+/* ---- the fused layer passes -------------------------------------------------------------
+ * All tensors are row-major and contiguous.  T = num_local_tokens, H = hidden, I = intermediate,
+ * El = num_local_experts, K = topk, MB = macrobatch_size, cap = schedule_capacity.  Pointer
+ * arrays `*_ptrs` hold ep_size device addresses, one per rank (own rank included). */
+
+typedef struct mok_layer_common {
+    int ep_size, ep_rank;
+    int num_local_tokens, hidden, intermediate, num_local_experts, topk;
+    int schedule_capacity, macrobatch_size, minibatch_size, num_comm_sms;
+    int has_swiglu_limit;
+    float swiglu_limit;
+    const int32_t* schedule_peer_rank;      /* [cap] */
+    const int32_t* schedule_peer_token_idx; /* [cap] */
+    const int32_t* num_tokens;              /* [1]   */
+    const int32_t* tokens_per_expert;       /* [El]  */
+    int32_t* status;                        /* [4] or NULL */
+} mok_layer_common;
+
+/* Forward, BF16 routed experts.
+ * Reference: mok/ops.py:371-514 (dispatch_mlp_swiglu_combine_fwd_bf16),
+ * csrc/mok_megakernel.cuh:1561-1851,1990-2100. */
+typedef struct mok_fwd_bf16_args {
+    mok_layer_common c;
+    const uint64_t* x_ptrs;              /* per-rank x buffers [T, H] bf16 */
+    const uint64_t* combine_buffer_ptrs; /* per-rank combine buffers [T*K, H] bf16 */
+    const void *w_shared_gate, *w_shared_up, *w_shared_down; /* [I,H] [I,H] [H,I] bf16 */
+    const void *w_routed_gate, *w_routed_up, *w_routed_down; /* [El,I,H] [El,I,H] [El,H,I] bf16 */
+    /* outputs */
+    void *x_routed;                               /* [MB, H] */
+    void *gate_shared, *up_shared, *hidden_shared; /* [T, I]  */
+    void *gate_routed, *up_routed, *hidden_routed; /* [MB, I] */
+    void *y_shared;                               /* [T, H]  */
+    void *y_routed;                               /* [MB, H] */
+} mok_fwd_bf16_args;
+int mok_fwd_bf16(const mok_fwd_bf16_args* args, void* stream);
+
+/* Backward, BF16 routed experts.  Mutates the saved routed activations when the schedule
+ * spans more than one macrobatch (forward replay), as the reference does.
+ * Reference: mok/ops.py:811-1008 (dispatch_mlp_swiglu_combine_bwd_bf16),
+ * csrc/mok_megakernel.cuh:2102-2544,2779-2967. */
+typedef struct mok_bwd_bf16_args {
+    mok_layer_common c;
+    const uint64_t* d_y_ptrs;                    /* per-rank upstream grads [T, H] bf16 */
+    const uint64_t* d_x_routed_buffer_ptrs;      /* per-rank [T*K, H] bf16 */
+    const uint64_t* router_weight_ptrs;          /* per-rank [T, K] f32 */
+    const uint64_t* d_router_weight_ptrs;        /* per-rank [T, K] f32 */
+    const uint64_t* x_ptrs;                      /* per-rank x [T, H] bf16 */
+    const void *w_shared_gate, *w_shared_up, *w_shared_down;
+    const void *w_routed_gate, *w_routed_up, *w_routed_down;
+    /* saved forward activations (routed ones are overwritten by replay) */
+    void *x_routed, *gate_routed, *up_routed, *hidden_routed;
+    const void *gate_shared, *up_shared, *hidden_shared;
+    /* outputs */
+    void *d_x_shared;                                     /* [T, H]  */
+    void *d_x_routed;                                     /* [MB, H] */
+    void *d_gate_shared, *d_up_shared, *d_hidden_shared;  /* [T, I]  */
+    void *d_gate_routed, *d_up_routed, *d_hidden_routed;  /* [MB, I] */
+    void *d_y_routed;                                     /* [MB, H] */
+    void *d_w_shared_gate, *d_w_shared_up, *d_w_shared_down;
+    void *d_w_routed_gate, *d_w_routed_up, *d_w_routed_down;
+    /* scratch: router weights per routed row [MB] f32, router-grad partials [MB, I/256] f32 */
+    float* router_weights_routed;
+    float* d_router_weight_partials;
+} mok_bwd_bf16_args;
+int mok_bwd_bf16(const mok_bwd_bf16_args* args, void* stream);
+
+/* Building block exposed for tests and tuning: C[M,N] (bf16) = A * B with fp32 accumulation on
+ * tcgen05.  a_mn_major / b_mn_major select the memory layout of the operands:
+ *   A: 0 = [M, K] row-major (K-major), 1 = [K, M] row-major (M-major)
+ *   B: 0 = [N, K] row-major (K-major), 1 = [K, N] row-major (N-major)
+ * M % 128 == 0, N % 256 == 0, K % 64 == 0. */
+int mok_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k,
+                  int a_mn_major, int b_mn_major, int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MOK_B200_H_ */

@@ -1,0 +1,32 @@
+// Parameters and launchers of the row-movement kernels (dispatch / combine), shared between
+// comm.cu and the layer orchestration in layer.cu.
+#pragma once
+
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace mok {
+
+struct RowMoveParams {
+    PeerPtrs peers;            // per-rank base of the remote [*, hidden] bf16 buffer
+    PeerPtrs scale_peers;      // dispatch<scale>: per-rank router weights [T*K] f32 (read)
+                               // combine+partials: per-rank d_router_weight [T*K] f32 (written)
+    void* local;               // local [row_limit, hidden] bf16 buffer (dispatch: out, combine: in)
+    const int* peer_rank;      // [capacity]
+    const int* peer_token_idx; // [capacity] = token * topk + k
+    const int* num_tokens;     // [1]
+    int capacity;
+    int row_offset;            // first schedule row of this macrobatch
+    int row_limit;             // macrobatch size
+    int hidden;
+    int row_divisor;           // dispatch: topk (route -> token row); 1 otherwise
+    float* row_scale_out;      // dispatch<scale>: [row_limit] router weight of every routed row
+    const float* partials;     // combine: [row_limit, partial_cols] router-gradient partial sums
+    int partial_cols;
+};
+
+int launch_dispatch_rows(const RowMoveParams& p, bool scale, int num_blocks, cudaStream_t stream);
+int launch_combine_rows(const RowMoveParams& p, int num_blocks, cudaStream_t stream);
+
+}  // namespace mok

@@ -1,0 +1,140 @@
+// Host side of the tcgen05 grouped GEMM: tensor-map construction, instantiation table, and the
+// plain-GEMM entry point used by the tests.
+#include "gemm.cuh"
+
+#include <mutex>
+
+namespace mok {
+
+namespace {
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* sym = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(sym);
+    });
+    return fn;
+}
+}  // namespace
+
+int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                 uint32_t box_inner, uint32_t box_outer, int elem_bytes) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (!fn) return MOK_ERR_CUDA;
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? MOK_OK : MOK_ERR_CUDA;
+}
+
+int device_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+namespace {
+template <int kA, int kB, int kEpi, bool kW>
+int launch_inst(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1, const CUtensorMap& b1, const GemmParams& p,
+                int grid, cudaStream_t stream) {
+    auto* kern = grouped_gemm_kernel<kA, kB, kEpi, kW>;
+    static bool configured[64] = {false};   // per instantiation and device: the attribute is sticky
+    int dev = 0;
+    MOK_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        MOK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(a0, b0, a1, b1, p);
+    MOK_CUDA_CHECK(cudaGetLastError());
+    return MOK_OK;
+}
+}  // namespace
+
+int launch_grouped_gemm(int a_major, int b_major, int epi, bool wgrad, const GemmOperands& ops, const GemmParams& p,
+                        int max_tiles, int max_ctas, cudaStream_t stream) {
+    if (max_tiles <= 0) return MOK_OK;
+    CUtensorMap a0, b0, a1, b1;
+    // A: K-major box {64 K, 128 rows}; M-major box {64 M, 64 K-rows}
+    const uint32_t a_box_outer = a_major == kMajorK ? kBlockM : kBlockK;
+    // B: K-major box {64 K, 256 rows} (128 when the tile is split into gate|up halves); N-major box {64 N, 64 K-rows}
+    const uint32_t b_box_outer = b_major == kMajorK ? (epi == kEpiSwigluFwd ? kBlockN / 2 : kBlockN) : kBlockK;
+    int rc;
+    if ((rc = make_tmap_2d(&a0, ops.a0, ops.a_inner, ops.a_outer, ops.a_inner * 2, 64, a_box_outer, 2))) return rc;
+    if ((rc = make_tmap_2d(&b0, ops.b0, ops.b_inner, ops.b_outer, ops.b_inner * 2, 64, b_box_outer, 2))) return rc;
+    if ((rc = make_tmap_2d(&a1, ops.a1 ? ops.a1 : ops.a0, ops.a_inner, ops.a_outer, ops.a_inner * 2, 64, a_box_outer, 2))) return rc;
+    if ((rc = make_tmap_2d(&b1, ops.b1 ? ops.b1 : ops.b0, ops.b_inner, ops.b_outer, ops.b_inner * 2, 64, b_box_outer, 2))) return rc;
+    int ctas = device_sm_count();
+    if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
+    const int grid = max_tiles < ctas ? max_tiles : ctas;
+
+    if (!wgrad && a_major == kMajorK && b_major == kMajorK && epi == kEpiStore)
+        return launch_inst<kMajorK, kMajorK, kEpiStore, false>(a0, b0, a1, b1, p, grid, stream);
+    if (!wgrad && a_major == kMajorK && b_major == kMajorK && epi == kEpiSwigluFwd)
+        return launch_inst<kMajorK, kMajorK, kEpiSwigluFwd, false>(a0, b0, a1, b1, p, grid, stream);
+    if (!wgrad && a_major == kMajorK && b_major == kMajorMN && epi == kEpiStore)
+        return launch_inst<kMajorK, kMajorMN, kEpiStore, false>(a0, b0, a1, b1, p, grid, stream);
+    if (!wgrad && a_major == kMajorK && b_major == kMajorMN && epi == kEpiSwigluBwd)
+        return launch_inst<kMajorK, kMajorMN, kEpiSwigluBwd, false>(a0, b0, a1, b1, p, grid, stream);
+    if (wgrad && a_major == kMajorMN && b_major == kMajorMN && epi == kEpiStore)
+        return launch_inst<kMajorMN, kMajorMN, kEpiStore, true>(a0, b0, a1, b1, p, grid, stream);
+    return MOK_ERR_UNSUPPORTED;
+}
+
+}  // namespace mok
+
+extern "C" int mok_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k, int a_mn_major, int b_mn_major,
+                             int32_t* status, void* stream) {
+    using namespace mok;
+    if (!a || !b || !c || m <= 0 || n <= 0 || k <= 0) return MOK_ERR_INVALID;
+    if (m % kBlockM || n % kBlockN || k % kBlockK) return MOK_ERR_INVALID;
+    GemmParams p{};
+    p.num_tokens = nullptr;
+    p.capacity = 0;
+    p.row_offset = 0;
+    p.tokens_per_expert = nullptr;
+    p.num_experts = 1;
+    p.n_tiles = n / kBlockN;
+    p.num_segs = 1;
+    p.out0 = static_cast<__nv_bfloat16*>(c);
+    p.ld_out = n;
+    p.status = status;
+    GemmOperands ops{};
+    ops.a0 = a; ops.b0 = b;
+    const bool wgrad = a_mn_major != 0;
+    if (!wgrad) {
+        p.rows_host = m; p.row_limit = m;
+        p.k_blocks_per_seg = k / kBlockK;
+        ops.a_inner = k; ops.a_outer = m;
+        if (b_mn_major) { ops.b_inner = n; ops.b_outer = k; p.b_rows_per_expert = k; }
+        else { ops.b_inner = k; ops.b_outer = n; p.b_rows_per_expert = n; }
+    } else {
+        if (!b_mn_major) return MOK_ERR_UNSUPPORTED;
+        p.rows_host = k; p.row_limit = k;       // contraction runs over the rows of both operands
+        p.m_tiles_w = m / kBlockM;
+        p.out_expert_stride = 0;
+        ops.a_inner = m; ops.a_outer = k;
+        ops.b_inner = n; ops.b_outer = k;
+    }
+    const int tiles = (m / kBlockM) * (n / kBlockN);
+    return launch_grouped_gemm(a_mn_major ? kMajorMN : kMajorK, b_mn_major ? kMajorMN : kMajorK, kEpiStore, wgrad, ops, p,
+                               tiles, 0, static_cast<cudaStream_t>(stream));
+}

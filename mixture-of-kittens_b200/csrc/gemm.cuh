@@ -1,0 +1,390 @@
+// Persistent grouped GEMM on the 5th-generation tensor cores (tcgen05) of sm_100a.
+//
+//   - operands are staged in shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, no
+//     cluster multicast), 4 stages of 128x64 (A) + 256x64 (B) bf16 = 48 KB each;
+//   - one elected thread issues tcgen05.mma (M=128, N=256, K=16 per instruction), fp32
+//     accumulators live in tensor memory, double-buffered (2 x 256 columns) so the epilogue of
+//     tile i overlaps the main loop of tile i+1;
+//   - four epilogue warps read the accumulator with tcgen05.ld and apply the fused epilogue:
+//     plain bf16 store (optionally accumulating), SwiGLU forward (gate|up halves of one tile),
+//     or SwiGLU backward with the router-gradient partial sums.
+//
+// Warp roles in a 192-thread CTA: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..5 = epilogue (TMEM lane quarter = warp id % 4).  One CTA per SM; tiles are assigned
+// round-robin (tile = blockIdx.x + i * gridDim.x), so results do not depend on timing.
+//
+// Row counts come from device memory (num_tokens / tokens_per_expert): nothing here needs a
+// host synchronisation.  Every wait is bounded; on expiry the CTA drains, frees its tensor
+// memory and reports MOK_STATUS_PIPELINE_TIMEOUT.
+#pragma once
+
+#include "common.cuh"
+
+namespace mok {
+
+enum : int { kMajorK = 0, kMajorMN = 1 };
+enum : int { kEpiStore = 0, kEpiSwigluFwd = 1, kEpiSwigluBwd = 2 };
+
+constexpr int kBlockM = 128;
+constexpr int kBlockN = 256;
+constexpr int kBlockK = 64;
+constexpr int kStages = 4;
+constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KB
+constexpr int kBBytes = kBlockN * kBlockK * 2;   // 32 KB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+constexpr int kMaxExperts = MOK_MAX_LOCAL_EXPERTS;
+constexpr int kGemmSmemBytes = kStages * kStageBytes + 256 + kMaxExperts * 4 + 1024;
+
+struct GemmParams {
+    // row domain
+    const int* num_tokens;         // device row count (schedule rows); nullptr -> rows_host
+    int rows_host;
+    int capacity;
+    int row_offset;                // first schedule row of the window (macrobatch) this launch covers
+    int row_limit;                 // window size in rows; buffers are indexed relative to the window
+    const int* tokens_per_expert;  // nullptr -> one group covering every row
+    int num_experts;
+    // tiling
+    int n_tiles;                   // output tiles along N
+    int m_tiles_w;                 // weight-gradient mode: output tiles along M
+    int k_blocks_per_seg;          // K / 64 per segment (ignored in weight-gradient mode)
+    int num_segs;                  // 1, or 2 for the two-GEMM accumulation d_gate*Wg + d_up*Wu
+    int b_rows_per_expert;         // rows between experts in B's tensor map
+    // epilogue
+    __nv_bfloat16* out0;           // store: C; swiglu fwd: gate; swiglu bwd: d_hidden
+    __nv_bfloat16* out1;           // swiglu fwd: up;   swiglu bwd: d_gate
+    __nv_bfloat16* out2;           // swiglu fwd: hidden; swiglu bwd: d_up
+    const __nv_bfloat16* in0;      // swiglu bwd: saved gate
+    const __nv_bfloat16* in1;      // swiglu bwd: saved up
+    int ld_out;
+    long long out_expert_stride;   // weight-gradient mode: elements between experts in out0
+    int accumulate;                // weight-gradient mode: add to the bf16 value already stored
+    const float* row_scale;        // swiglu bwd: router weight per routed row (nullptr for the shared expert)
+    float* partials;               // swiglu bwd: [rows, n_tiles] router-gradient partial sums
+    float limit;
+    int has_limit;
+    int* status;
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    return __fdividef(g, 1.0f + __expf(-g)) * u;
+}
+
+template <int kAMajor, int kBMajor, int kEpi, bool kWgrad>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+                    const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+                    const GemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
+    uint64_t* empty_bar = full_bar + kStages;
+    uint64_t* tfull_bar = empty_bar + kStages;
+    uint64_t* tempty_bar = tfull_bar + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* s_end = reinterpret_cast<int*>(smem + kStages * kStageBytes + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int E = p.tokens_per_expert ? p.num_experts : 1;
+
+    // inclusive prefix of padded rows per expert
+    if (p.tokens_per_expert) {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) s_end[e] = p.tokens_per_expert[e];
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (warp == 0 && p.tokens_per_expert) {
+        const int per = (E + 31) / 32;
+        int sum = 0;
+        for (int j = 0; j < per; ++j) { const int e = lane * per + j; if (e < E) sum += s_end[e]; }
+        int incl = sum;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) { const int n = __shfl_up_sync(0xffffffffu, incl, off); if (lane >= off) incl += n; }
+        int run = incl - sum;
+        for (int j = 0; j < per; ++j) { const int e = lane * per + j; if (e < E) { run += s_end[e]; s_end[e] = run; } }
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_total = p.num_tokens ? min(*p.num_tokens, p.capacity) : p.rows_host;
+    const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
+    // a weight-gradient launch that only accumulates has nothing to do on an empty window
+    const int num_tiles = kWgrad ? ((p.accumulate && win_rows == 0) ? 0 : E * p.m_tiles_w * p.n_tiles)
+                                 : (win_rows / kBlockM) * p.n_tiles;
+
+    // tile -> coordinates.  a_row: first A/C row (window-relative); k_row0/k_blocks: contraction range
+    auto decode = [&](int tile, int& m_idx, int& n_idx, int& expert, int& k_row0, int& k_blocks) {
+        if constexpr (kWgrad) {
+            const int per_e = p.m_tiles_w * p.n_tiles;
+            expert = tile / per_e;
+            const int r = tile - expert * per_e;
+            m_idx = r / p.n_tiles;
+            n_idx = r - m_idx * p.n_tiles;
+            int s = 0, e_end = n_total;
+            if (p.tokens_per_expert) { s = expert ? s_end[expert - 1] : 0; e_end = min(s_end[expert], n_total); }
+            const int lo = max(s, p.row_offset), hi = min(e_end, p.row_offset + win_rows);
+            k_row0 = lo - p.row_offset;
+            k_blocks = hi > lo ? (hi - lo) / kBlockK : 0;
+        } else {
+            m_idx = tile / p.n_tiles;
+            n_idx = tile - m_idx * p.n_tiles;
+            expert = 0;
+            if (p.tokens_per_expert) {
+                const int g = p.row_offset + m_idx * kBlockM;
+                int lo = 0, hi = E - 1;
+                while (lo < hi) { const int mid = (lo + hi) >> 1; if (s_end[mid] > g) hi = mid; else lo = mid + 1; }
+                expert = lo;
+            }
+            k_row0 = 0;
+            k_blocks = p.k_blocks_per_seg * p.num_segs;
+        }
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmA0); tma_prefetch_desc(&tmB0);
+            if (p.num_segs > 1) { tma_prefetch_desc(&tmA1); }
+            if (p.num_segs > 1 || kEpi == kEpiSwigluFwd) { tma_prefetch_desc(&tmB1); }
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int m_idx, n_idx, expert, k_row0, k_blocks;
+                decode(tile, m_idx, n_idx, expert, k_row0, k_blocks);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* sa = smem + stage * kStageBytes;
+                    uint8_t* sb = sa + kABytes;
+                    mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+                    const int seg = (!kWgrad && kb >= p.k_blocks_per_seg) ? 1 : 0;
+                    const int kk = (kWgrad ? kb : kb - seg * p.k_blocks_per_seg) * kBlockK;
+                    const CUtensorMap* ma = seg ? &tmA1 : &tmA0;
+                    const CUtensorMap* mb = seg ? &tmB1 : &tmB0;
+                    // A
+                    if constexpr (kAMajor == kMajorK) {
+                        tma_load_2d(sa, ma, &full_bar[stage], kk, m_idx * kBlockM);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < kBlockM / 64; ++j)
+                            tma_load_2d(sa + j * (kBlockK * 128), ma, &full_bar[stage], m_idx * kBlockM + j * 64, k_row0 + kk);
+                    }
+                    // B
+                    if constexpr (kBMajor == kMajorK) {
+                        if constexpr (kEpi == kEpiSwigluFwd) {
+                            const int y = expert * p.b_rows_per_expert + n_idx * (kBlockN / 2);
+                            tma_load_2d(sb, &tmB0, &full_bar[stage], kk, y);
+                            tma_load_2d(sb + kBBytes / 2, &tmB1, &full_bar[stage], kk, y);
+                        } else {
+                            tma_load_2d(sb, mb, &full_bar[stage], kk, expert * p.b_rows_per_expert + n_idx * kBlockN);
+                        }
+                    } else {
+                        const int y = kWgrad ? (k_row0 + kk) : (expert * p.b_rows_per_expert + kk);
+#pragma unroll
+                        for (int j = 0; j < kBlockN / 64; ++j)
+                            tma_load_2d(sb + j * (kBlockK * 128), mb, &full_bar[stage], n_idx * kBlockN + j * 64, y);
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_bf16(kBlockM, kBlockN, kAMajor, kBMajor);
+            constexpr uint32_t a_lbo = kAMajor == kMajorK ? 16 : kBlockK * 128;
+            constexpr uint32_t b_lbo = kBMajor == kMajorK ? 16 : kBlockK * 128;
+            constexpr uint32_t a_kstep = kAMajor == kMajorK ? 32 : 2048;   // bytes per K=16 step
+            constexpr uint32_t b_kstep = kBMajor == kMajorK ? 32 : 2048;
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                int m_idx, n_idx, expert, k_row0, k_blocks;
+                decode(tile, m_idx, n_idx, expert, k_row0, k_blocks);
+                const int buf = it & 1;
+                const uint32_t acc_phase = (it >> 1) & 1;
+                if (!mbar_wait(&tempty_bar[buf], acc_phase ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * kBlockN;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+                    const uint32_t sb = sa + kABytes;
+                    const uint64_t adesc = make_smem_desc(sa, a_lbo, 1024);
+                    const uint64_t bdesc = make_smem_desc(sb, b_lbo, 1024);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k) {
+                        umma_f16(d_tmem, adesc + ((k * a_kstep) >> 4), bdesc + ((k * b_kstep) >> 4), idesc,
+                                 (kb > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                if (k_blocks > 0) umma_commit(&tfull_bar[buf]);
+                else mbar_arrive(&tfull_bar[buf]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const int quarter = warp & 3;
+        const int r_in_tile = quarter * 32 + lane;
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            int m_idx, n_idx, expert, k_row0, k_blocks;
+            decode(tile, m_idx, n_idx, expert, k_row0, k_blocks);
+            const int buf = it & 1;
+            const uint32_t acc_phase = (it >> 1) & 1;
+            if (!mbar_wait(&tfull_bar[buf], acc_phase, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlockN;
+            const size_t row = static_cast<size_t>(m_idx) * kBlockM + r_in_tile;
+
+            if constexpr (kEpi == kEpiStore) {
+                __nv_bfloat16* dst = p.out0 + (kWgrad ? static_cast<size_t>(expert) * p.out_expert_stride : 0) +
+                                     row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN;
+                const bool skip_store = kWgrad && p.accumulate && k_blocks == 0;   // adding zero: leave as is
+#pragma unroll 1
+                for (int c = 0; c < (skip_store ? 0 : kBlockN / 32); ++c) {
+                    uint32_t acc[32];
+                    if (k_blocks > 0) { tmem_ld_32x32(t_addr + c * 32, acc); tmem_ld_wait(); }
+                    else {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) acc[i] = 0u;
+                    }
+                    uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(acc[v * 8 + i]);
+                        if (kWgrad && p.accumulate) {
+                            const uint4 old = d4[v];
+                            const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) { const float2 q = unpack_bf16(o[i]); f[2 * i] += q.x; f[2 * i + 1] += q.y; }
+                        }
+                        d4[v] = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+                    }
+                }
+            } else if constexpr (kEpi == kEpiSwigluFwd) {
+                const size_t off = row * p.ld_out + static_cast<size_t>(n_idx) * (kBlockN / 2);
+#pragma unroll 1
+                for (int c = 0; c < kBlockN / 64; ++c) {
+                    uint32_t g[32], u[32];
+                    tmem_ld_32x32(t_addr + c * 32, g);
+                    tmem_ld_32x32(t_addr + kBlockN / 2 + c * 32, u);
+                    tmem_ld_wait();
+                    uint4* dg = reinterpret_cast<uint4*>(p.out0 + off + c * 32);
+                    uint4* du = reinterpret_cast<uint4*>(p.out1 + off + c * 32);
+                    uint4* dh = reinterpret_cast<uint4*>(p.out2 + off + c * 32);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        uint32_t gw[4], uw[4], hw[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            gw[i] = pack_bf16(__uint_as_float(g[v * 8 + 2 * i]), __uint_as_float(g[v * 8 + 2 * i + 1]));
+                            uw[i] = pack_bf16(__uint_as_float(u[v * 8 + 2 * i]), __uint_as_float(u[v * 8 + 2 * i + 1]));
+                            float2 gf = unpack_bf16(gw[i]), uf = unpack_bf16(uw[i]);
+                            if (p.has_limit) {
+                                gf.x = fminf(gf.x, p.limit); gf.y = fminf(gf.y, p.limit);
+                                uf.x = fminf(fmaxf(uf.x, -p.limit), p.limit); uf.y = fminf(fmaxf(uf.y, -p.limit), p.limit);
+                            }
+                            hw[i] = pack_bf16(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
+                        }
+                        dg[v] = make_uint4(gw[0], gw[1], gw[2], gw[3]);
+                        du[v] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
+                        dh[v] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                    }
+                }
+            } else {
+                // SwiGLU backward on the d_hidden tile just computed
+                const size_t off = row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN;
+                float inv_w = 0.0f;
+                if (p.row_scale) { const float w = p.row_scale[row]; inv_w = w > 0.0f ? 1.0f / w : 0.0f; }
+                float partial = 0.0f;
+#pragma unroll 1
+                for (int c = 0; c < kBlockN / 32; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld_32x32(t_addr + c * 32, acc);
+                    const uint4* sg = reinterpret_cast<const uint4*>(p.in0 + off + c * 32);
+                    const uint4* su = reinterpret_cast<const uint4*>(p.in1 + off + c * 32);
+                    uint4 gv[4], uv[4];
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) { gv[v] = sg[v]; uv[v] = su[v]; }
+                    tmem_ld_wait();
+                    uint4* dh = reinterpret_cast<uint4*>(p.out0 + off + c * 32);
+                    uint4* dg = reinterpret_cast<uint4*>(p.out1 + off + c * 32);
+                    uint4* du = reinterpret_cast<uint4*>(p.out2 + off + c * 32);
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const uint32_t gin[4] = {gv[v].x, gv[v].y, gv[v].z, gv[v].w};
+                        const uint32_t uin[4] = {uv[v].x, uv[v].y, uv[v].z, uv[v].w};
+                        uint32_t hw[4], gw[4], uw[4];
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            hw[i] = pack_bf16(__uint_as_float(acc[v * 8 + 2 * i]), __uint_as_float(acc[v * 8 + 2 * i + 1]));
+                            const float2 dhf = unpack_bf16(hw[i]);
+                            float2 gf = unpack_bf16(gin[i]), uf = unpack_bf16(uin[i]);
+                            bool gm0 = true, gm1 = true, um0 = true, um1 = true;
+                            if (p.has_limit) {
+                                gm0 = gf.x <= p.limit; gm1 = gf.y <= p.limit;
+                                um0 = uf.x >= -p.limit && uf.x <= p.limit; um1 = uf.y >= -p.limit && uf.y <= p.limit;
+                                gf.x = fminf(gf.x, p.limit); gf.y = fminf(gf.y, p.limit);
+                                uf.x = fminf(fmaxf(uf.x, -p.limit), p.limit); uf.y = fminf(fmaxf(uf.y, -p.limit), p.limit);
+                            }
+                            const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x)), s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+                            const float silu0 = gf.x * s0, silu1 = gf.y * s1;
+                            const float ds0 = (1.0f - silu0) * s0 + silu0, ds1 = (1.0f - silu1) * s1 + silu1;
+                            gw[i] = pack_bf16(gm0 ? ds0 * uf.x * dhf.x : 0.0f, gm1 ? ds1 * uf.y * dhf.y : 0.0f);
+                            uw[i] = pack_bf16(um0 ? silu0 * dhf.x : 0.0f, um1 ? silu1 * dhf.y : 0.0f);
+                            partial += dhf.x * inv_w * (silu0 * uf.x) + dhf.y * inv_w * (silu1 * uf.y);
+                        }
+                        dh[v] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                        dg[v] = make_uint4(gw[0], gw[1], gw[2], gw[3]);
+                        du[v] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
+                    }
+                }
+                if (p.partials) p.partials[row * p.n_tiles + n_idx] = partial;
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+    if (threadIdx.x == 0 && *abort_flag) report_status(p.status, MOK_STATUS_PIPELINE_TIMEOUT, warp);
+}
+
+// host side ---------------------------------------------------------------------------------
+int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
+                 uint32_t box_inner, uint32_t box_outer, int elem_bytes);
+int device_sm_count();
+
+struct GemmOperands {
+    const void* a0; const void* b0; const void* a1; const void* b1;   // a1/b1: second segment or "up" weights
+    uint64_t a_inner, a_outer;   // tensor-map extents of A (elements, rows)
+    uint64_t b_inner, b_outer;
+};
+// a_major/b_major/epi/wgrad select the instantiation; `max_ctas` caps the grid (0 = all SMs)
+int launch_grouped_gemm(int a_major, int b_major, int epi, bool wgrad, const GemmOperands& ops, const GemmParams& p,
+                        int max_tiles, int max_ctas, cudaStream_t stream);
+
+}  // namespace mok

@@ -1,0 +1,290 @@
+// Layer passes: forward and backward of the expert-parallel MoE layer with BF16 routed experts.
+// Each pass is a short, fixed sequence of launches on the caller's stream; all row counts are
+// read on the device (num_tokens, tokens_per_expert), so nothing here synchronises with the host.
+//
+// Forward, per macrobatch window (last window first, so window 0's activations are the ones
+// left in the buffers for backward — same contract as the reference megakernel):
+//   dispatch rows  ->  [gate|up GEMM + SwiGLU]  ->  down GEMM  ->  combine rows
+// plus the dense shared expert on the local tokens.
+// Backward, per window (first window first; later windows replay dispatch + gate/up):
+//   reverse-combine (w * d_y)  ->  [dgrad down + SwiGLU backward + router-grad partials]
+//   ->  dgrad gate+up (one accumulator)  ->  reverse-dispatch (+ router grads)  ->  3 wgrads
+#include "comm.cuh"
+#include "gemm.cuh"
+
+namespace mok {
+namespace {
+
+struct Dims {
+    int W, rank, T, H, I, El, K, cap, MB;
+};
+
+int check_common(const mok_layer_common& c, Dims& d) {
+    d = Dims{c.ep_size, c.ep_rank, c.num_local_tokens, c.hidden, c.intermediate, c.num_local_experts, c.topk,
+             c.schedule_capacity, c.macrobatch_size};
+    if (d.W < 1 || d.W > MOK_MAX_PEERS || d.rank < 0 || d.rank >= d.W) return MOK_ERR_INVALID;
+    if (d.T <= 0 || d.T % 256 || d.H <= 0 || d.H % 256 || d.I <= 0 || d.I % 256) return MOK_ERR_INVALID;
+    if (d.El < 1 || d.El > MOK_MAX_LOCAL_EXPERTS || d.K < 1 || d.K > 255) return MOK_ERR_INVALID;
+    if (d.cap <= 0 || d.cap % 256 || d.MB <= 0 || d.MB % 256) return MOK_ERR_INVALID;
+    if (c.minibatch_size <= 0 || c.minibatch_size % 256 || d.MB % c.minibatch_size) return MOK_ERR_INVALID;
+    if (!c.schedule_peer_rank || !c.schedule_peer_token_idx || !c.num_tokens || !c.tokens_per_expert) return MOK_ERR_INVALID;
+    return MOK_OK;
+}
+
+int fill_peers(PeerPtrs& out, const uint64_t* ptrs, int W) {
+    if (!ptrs) return MOK_ERR_INVALID;
+    for (int i = 0; i < W; ++i) {
+        if (!ptrs[i]) return MOK_ERR_INVALID;
+        out.p[i] = reinterpret_cast<void*>(ptrs[i]);
+    }
+    return MOK_OK;
+}
+
+GemmParams base_params(const mok_layer_common& c, bool routed, int off, int limit) {
+    GemmParams p{};
+    if (routed) {
+        p.num_tokens = c.num_tokens;
+        p.capacity = c.schedule_capacity;
+        p.tokens_per_expert = c.tokens_per_expert;
+        p.num_experts = c.num_local_experts;
+        p.row_offset = off;
+        p.row_limit = limit;
+    } else {
+        p.rows_host = c.num_local_tokens;
+        p.row_limit = c.num_local_tokens;
+        p.num_experts = 1;
+    }
+    p.num_segs = 1;
+    p.limit = c.swiglu_limit;
+    p.has_limit = c.has_swiglu_limit;
+    p.status = c.status;
+    return p;
+}
+
+#define MOK_TRY(expr) do { int rc__ = (expr); if (rc__ != MOK_OK) return rc__; } while (0)
+
+// gate|up GEMM with fused SwiGLU: A [rows, H] K-major, B = (Wg, Wu) [E*I, H] K-major
+int run_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int off, int limit, const void* a, int a_rows,
+                const void* wg, const void* wu, void* gate, void* up, void* hidden, cudaStream_t s) {
+    GemmParams p = base_params(c, routed, off, limit);
+    p.n_tiles = d.I / (kBlockN / 2);
+    p.k_blocks_per_seg = d.H / kBlockK;
+    p.b_rows_per_expert = d.I;
+    p.out0 = static_cast<__nv_bfloat16*>(gate);
+    p.out1 = static_cast<__nv_bfloat16*>(up);
+    p.out2 = static_cast<__nv_bfloat16*>(hidden);
+    p.ld_out = d.I;
+    GemmOperands o{};
+    o.a0 = a; o.b0 = wg; o.b1 = wu;
+    o.a_inner = d.H; o.a_outer = a_rows;
+    o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.I;
+    return launch_grouped_gemm(kMajorK, kMajorK, kEpiSwigluFwd, false, o, p, (limit / kBlockM) * p.n_tiles, 0, s);
+}
+
+// down GEMM: A = hidden [rows, I] K-major, B = Wd [E*H, I] K-major
+int run_down(const mok_layer_common& c, const Dims& d, bool routed, int off, int limit, const void* hidden, int a_rows,
+             const void* wd, void* y, cudaStream_t s) {
+    GemmParams p = base_params(c, routed, off, limit);
+    p.n_tiles = d.H / kBlockN;
+    p.k_blocks_per_seg = d.I / kBlockK;
+    p.b_rows_per_expert = d.H;
+    p.out0 = static_cast<__nv_bfloat16*>(y);
+    p.ld_out = d.H;
+    GemmOperands o{};
+    o.a0 = hidden; o.b0 = wd;
+    o.a_inner = d.I; o.a_outer = a_rows;
+    o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.H;
+    return launch_grouped_gemm(kMajorK, kMajorK, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0, s);
+}
+
+// d_hidden = d_y @ Wd (B is [E*H, I] read N-major), fused SwiGLU backward
+int run_dgrad_down(const mok_layer_common& c, const Dims& d, bool routed, int off, int limit, const void* d_y, int a_rows,
+                   const void* wd, const void* gate, const void* up, void* d_hidden, void* d_gate, void* d_up,
+                   const float* row_scale, float* partials, cudaStream_t s) {
+    GemmParams p = base_params(c, routed, off, limit);
+    p.n_tiles = d.I / kBlockN;
+    p.k_blocks_per_seg = d.H / kBlockK;
+    p.b_rows_per_expert = d.H;
+    p.out0 = static_cast<__nv_bfloat16*>(d_hidden);
+    p.out1 = static_cast<__nv_bfloat16*>(d_gate);
+    p.out2 = static_cast<__nv_bfloat16*>(d_up);
+    p.in0 = static_cast<const __nv_bfloat16*>(gate);
+    p.in1 = static_cast<const __nv_bfloat16*>(up);
+    p.ld_out = d.I;
+    p.row_scale = row_scale;
+    p.partials = partials;
+    GemmOperands o{};
+    o.a0 = d_y; o.b0 = wd;
+    o.a_inner = d.H; o.a_outer = a_rows;
+    o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.H;
+    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiSwigluBwd, false, o, p, (limit / kBlockM) * p.n_tiles, 0, s);
+}
+
+// d_x = d_gate @ Wg + d_up @ Wu in one accumulator (B = [E*I, H] read N-major)
+int run_dgrad_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int off, int limit, const void* d_gate,
+                      const void* d_up, int a_rows, const void* wg, const void* wu, void* d_x, cudaStream_t s) {
+    GemmParams p = base_params(c, routed, off, limit);
+    p.n_tiles = d.H / kBlockN;
+    p.k_blocks_per_seg = d.I / kBlockK;
+    p.num_segs = 2;
+    p.b_rows_per_expert = d.I;
+    p.out0 = static_cast<__nv_bfloat16*>(d_x);
+    p.ld_out = d.H;
+    GemmOperands o{};
+    o.a0 = d_gate; o.a1 = d_up; o.b0 = wg; o.b1 = wu;
+    o.a_inner = d.I; o.a_outer = a_rows;
+    o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.I;
+    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0, s);
+}
+
+// dW[e] [m, n] = A[rows_e, m]^T @ B[rows_e, n]; both operands are read MN-major straight from the
+// row-major activations
+int run_wgrad(const mok_layer_common& c, bool routed, int off, int limit, const void* a, int m, const void* b, int n,
+              int rows, void* dw, int accumulate, cudaStream_t s) {
+    GemmParams p = base_params(c, routed, off, limit);
+    p.m_tiles_w = m / kBlockM;
+    p.n_tiles = n / kBlockN;
+    p.out0 = static_cast<__nv_bfloat16*>(dw);
+    p.ld_out = n;
+    p.out_expert_stride = static_cast<long long>(m) * n;
+    p.accumulate = accumulate;
+    GemmOperands o{};
+    o.a0 = a; o.b0 = b;
+    o.a_inner = m; o.a_outer = rows;
+    o.b_inner = n; o.b_outer = rows;
+    const int experts = routed ? c.num_local_experts : 1;
+    return launch_grouped_gemm(kMajorMN, kMajorMN, kEpiStore, true, o, p, experts * p.m_tiles_w * p.n_tiles, 0, s);
+}
+
+RowMoveParams row_move(const mok_layer_common& c, const Dims& d, int off, int limit, void* local) {
+    RowMoveParams r{};
+    r.local = local;
+    r.peer_rank = c.schedule_peer_rank;
+    r.peer_token_idx = c.schedule_peer_token_idx;
+    r.num_tokens = c.num_tokens;
+    r.capacity = d.cap;
+    r.row_offset = off;
+    r.row_limit = limit;
+    r.hidden = d.H;
+    r.row_divisor = 1;
+    return r;
+}
+
+}  // namespace
+}  // namespace mok
+
+using namespace mok;
+
+extern "C" int mok_fwd_bf16(const mok_fwd_bf16_args* a, void* stream) {
+    if (!a) return MOK_ERR_INVALID;
+    Dims d;
+    MOK_TRY(check_common(a->c, d));
+    const mok_layer_common& c = a->c;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    PeerPtrs x_peers{}, combine_peers{};
+    MOK_TRY(fill_peers(x_peers, a->x_ptrs, d.W));
+    MOK_TRY(fill_peers(combine_peers, a->combine_buffer_ptrs, d.W));
+    const void* x_local = x_peers.p[d.rank];
+    const int move_blocks = device_sm_count() * 4;
+
+    // shared expert on the local tokens
+    MOK_TRY(run_gate_up(c, d, false, 0, d.T, x_local, d.T, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
+                        a->hidden_shared, s));
+    MOK_TRY(run_down(c, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
+
+    const int n_macro = (d.cap + d.MB - 1) / d.MB;
+    for (int m = n_macro - 1; m >= 0; --m) {
+        const int off = m * d.MB;
+        const int limit = std::min(d.MB, d.cap - off);
+        RowMoveParams disp = row_move(c, d, off, limit, a->x_routed);
+        disp.peers = x_peers;
+        disp.row_divisor = d.K;
+        MOK_TRY(launch_dispatch_rows(disp, false, move_blocks, s));
+        MOK_TRY(run_gate_up(c, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up, a->gate_routed,
+                            a->up_routed, a->hidden_routed, s));
+        MOK_TRY(run_down(c, d, true, off, limit, a->hidden_routed, d.MB, a->w_routed_down, a->y_routed, s));
+        RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
+        comb.peers = combine_peers;
+        MOK_TRY(launch_combine_rows(comb, move_blocks, s));
+    }
+    return MOK_OK;
+}
+
+extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
+    if (!a) return MOK_ERR_INVALID;
+    Dims d;
+    MOK_TRY(check_common(a->c, d));
+    const mok_layer_common& c = a->c;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    PeerPtrs dy_peers{}, dxr_peers{}, rw_peers{}, drw_peers{}, x_peers{};
+    MOK_TRY(fill_peers(dy_peers, a->d_y_ptrs, d.W));
+    MOK_TRY(fill_peers(dxr_peers, a->d_x_routed_buffer_ptrs, d.W));
+    MOK_TRY(fill_peers(rw_peers, a->router_weight_ptrs, d.W));
+    MOK_TRY(fill_peers(drw_peers, a->d_router_weight_ptrs, d.W));
+    MOK_TRY(fill_peers(x_peers, a->x_ptrs, d.W));
+    if (!a->router_weights_routed || !a->d_router_weight_partials) return MOK_ERR_INVALID;
+    const void* dy_local = dy_peers.p[d.rank];
+    const void* x_local = x_peers.p[d.rank];
+    const int move_blocks = device_sm_count() * 4;
+    const int partial_cols = d.I / kBlockN;
+
+    // shared expert
+    MOK_TRY(run_dgrad_down(c, d, false, 0, d.T, dy_local, d.T, a->w_shared_down, a->gate_shared, a->up_shared,
+                           a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, nullptr, s));
+    MOK_TRY(run_dgrad_gate_up(c, d, false, 0, d.T, a->d_gate_shared, a->d_up_shared, d.T, a->w_shared_gate, a->w_shared_up,
+                              a->d_x_shared, s));
+    MOK_TRY(run_wgrad(c, false, 0, d.T, dy_local, d.H, a->hidden_shared, d.I, d.T, a->d_w_shared_down, 0, s));
+    MOK_TRY(run_wgrad(c, false, 0, d.T, a->d_gate_shared, d.I, x_local, d.H, d.T, a->d_w_shared_gate, 0, s));
+    MOK_TRY(run_wgrad(c, false, 0, d.T, a->d_up_shared, d.I, x_local, d.H, d.T, a->d_w_shared_up, 0, s));
+
+    const int n_macro = (d.cap + d.MB - 1) / d.MB;
+    for (int m = 0; m < n_macro; ++m) {
+        const int off = m * d.MB;
+        const int limit = std::min(d.MB, d.cap - off);
+        if (m > 0) {   // replay the forward of this window into the saved-activation buffers
+            RowMoveParams disp = row_move(c, d, off, limit, a->x_routed);
+            disp.peers = x_peers;
+            disp.row_divisor = d.K;
+            MOK_TRY(launch_dispatch_rows(disp, false, move_blocks, s));
+            MOK_TRY(run_gate_up(c, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up, a->gate_routed,
+                                a->up_routed, a->hidden_routed, s));
+        }
+        RowMoveParams rc = row_move(c, d, off, limit, a->d_y_routed);
+        rc.peers = dy_peers;
+        rc.scale_peers = rw_peers;
+        rc.row_divisor = d.K;
+        rc.row_scale_out = a->router_weights_routed;
+        MOK_TRY(launch_dispatch_rows(rc, true, move_blocks, s));
+        MOK_TRY(run_dgrad_down(c, d, true, off, limit, a->d_y_routed, d.MB, a->w_routed_down, a->gate_routed, a->up_routed,
+                               a->d_hidden_routed, a->d_gate_routed, a->d_up_routed, a->router_weights_routed,
+                               a->d_router_weight_partials, s));
+        MOK_TRY(run_dgrad_gate_up(c, d, true, off, limit, a->d_gate_routed, a->d_up_routed, d.MB, a->w_routed_gate,
+                                  a->w_routed_up, a->d_x_routed, s));
+        RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
+        rd.peers = dxr_peers;
+        rd.scale_peers = drw_peers;
+        rd.partials = a->d_router_weight_partials;
+        rd.partial_cols = partial_cols;
+        MOK_TRY(launch_combine_rows(rd, move_blocks, s));
+        const int acc = m > 0 ? 1 : 0;
+        MOK_TRY(run_wgrad(c, true, off, limit, a->d_y_routed, d.H, a->hidden_routed, d.I, d.MB, a->d_w_routed_down, acc, s));
+        MOK_TRY(run_wgrad(c, true, off, limit, a->d_gate_routed, d.I, a->x_routed, d.H, d.MB, a->d_w_routed_gate, acc, s));
+        MOK_TRY(run_wgrad(c, true, off, limit, a->d_up_routed, d.I, a->x_routed, d.H, d.MB, a->d_w_routed_up, acc, s));
+    }
+    return MOK_OK;
+}
+
+extern "C" int mok_version(void) { return 100; }
+
+extern "C" const char* mok_error_string(int code) {
+    switch (code) {
+        case MOK_OK: return "ok";
+        case MOK_ERR_INVALID: return "invalid argument";
+        case MOK_ERR_CUDA: return "CUDA call failed";
+        case MOK_ERR_UNSUPPORTED: return "unsupported shape or mode";
+        case MOK_STATUS_SCHEDULE_OVERFLOW: return "schedule capacity exceeded";
+        case MOK_STATUS_BARRIER_TIMEOUT: return "device barrier timed out";
+        case MOK_STATUS_PIPELINE_TIMEOUT: return "kernel pipeline wait timed out";
+        default: return "unknown";
+    }
+}

@@ -1,0 +1,55 @@
+"""CPU: the C-ABI library loads and exports every symbol include/mok_b200.h declares; argument
+errors the host can detect come back as codes without touching a GPU."""
+import ctypes
+import os
+import re
+
+from tests.conftest import ROOT
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "mok_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(mok_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    import mok
+    names = _declared_symbols()
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(mok._lib.lib, n), f"{n} declared in mok_b200.h but not exported"
+
+
+def test_version_and_error_strings():
+    import mok
+    assert mok._lib.mok_version() >= 100
+    assert mok._lib.mok_error_string(-1) == b"invalid argument"
+    assert mok._lib.mok_error_string(1) == b"schedule capacity exceeded"
+
+
+def test_host_detected_argument_errors():
+    import mok
+    L = mok._lib
+    assert L.mok_schedule_scratch_bytes(8, 32) == (8 * 256 * 32 + 8 * 32) * 4
+    assert L.mok_schedule(None, 4, 512, 2, 4, 4096, 0, None, None, None, None, None, 0, None, None) == -1
+    assert L.mok_mxfp8_quantize(None, 1, 128, 128, None, None, None, None, None) == -1
+    assert L.mok_gemm_bf16(ctypes.c_void_p(16), ctypes.c_void_p(16), ctypes.c_void_p(16), 100, 256, 64, 0, 0, None, None) == -1
+    assert L.mok_fwd_bf16(None, None) == -1
+    assert L.mok_barrier_all(None, None, 4, None, None, 0, None) == -1
+
+
+def test_struct_sizes_match_header():
+    """The ctypes mirrors must have the same size as the C structs (checked with gcc)."""
+    import subprocess
+    import tempfile
+    import mok
+    src = '#include <stdio.h>\n#include "mok_b200.h"\nint main(){printf("%zu %zu %zu", sizeof(mok_layer_common), sizeof(mok_fwd_bf16_args), sizeof(mok_bwd_bf16_args));return 0;}\n'
+    with tempfile.TemporaryDirectory() as d:
+        c = os.path.join(d, "s.c")
+        open(c, "w").write(src)
+        exe = os.path.join(d, "s")
+        subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
+        sizes = [int(v) for v in subprocess.check_output([exe]).split()]
+    L = mok._lib
+    assert sizes == [ctypes.sizeof(L.LayerCommon), ctypes.sizeof(L.FwdBf16Args), ctypes.sizeof(L.BwdBf16Args)]
