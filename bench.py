@@ -1,0 +1,329 @@
+"""Benchmark of the MoE-layer hot path (schedule -> dispatch -> grouped SwiGLU FFN -> combine).
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+N = 1   workload "C2": BF16 forward, EP=1, T=16384 tokens, hidden 2048, 128 experts, top-8,
+        intermediate 768 (router: x @ W_r^T, W_r ~ N(0, 0.02), softmax, top-8, renormalise).
+        A step = build_schedule + forward, as the reference times its forward
+        (benchmarks/bench_mok.py:56-57 in Mixture-of-Kittens).
+N > 1   workload "C3": BF16 forward + backward, EP=N, 16384 tokens per rank, hidden 4096,
+        64 experts split over the ranks, top-6, intermediate 1536, uniform-random router logits,
+        minibatch 4096, macrobatch 131072.  Launched by torchrun, one rank per GPU; NCCL only
+        bootstraps the process group and the symmetric-memory rendezvous.
+
+One JSON line is printed by rank 0.  `value` is TFLOP/s summed over the N GPUs with inputs
+resident in HBM, FLOPs counted as the reference does (6*(T + T*K)*H*I forward, 3x that for
+forward+backward, padding and replay not counted).  `e2e` is the same metric through
+mok.functional with the step's inputs copied from pinned host memory and its results copied back
+inside the timed region.  `roofline` describes the dominant kernel (the routed gate|up grouped
+GEMM with fused SwiGLU) from CUDA events recorded around its launches inside the timed region.
+`cpu_baseline` / `--impl reference` time the CPU oracle (a port of the reference's pure-PyTorch
+test oracle) on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "mixture-of-kittens_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+METRIC = "MoE layer TFLOP/s (reference FLOP convention), BF16"
+UNIT = "TFLOP/s"
+
+WORKLOADS = {
+    "C2": dict(T=16384, H=2048, I=768, E=128, K=8, router="linear", backward=False,
+               minibatch=4096, macrobatch=262144, multiplier=0.5,
+               desc="BF16 forward, EP=1, T=16384, H=2048, E=128, top-8, I=768"),
+    "C3": dict(T=16384, H=4096, I=1536, E=64, K=6, router="uniform", backward=True,
+               minibatch=4096, macrobatch=131072, multiplier=0.5,
+               desc="BF16 fwd+bwd, 16384 tokens/rank, H=4096, 64 experts, top-6, I=1536"),
+}
+# DRAM bytes per launch of the dominant kernel from the ncu capture summarised under profiles/
+# (filled in per workload once captured; None = not captured)
+NCU_TRAFFIC_BYTES = {"C2": None, "C3": None}
+
+
+def layer_flops(T, K, H, I, backward):
+    f = 6.0 * (T + T * K) * H * I
+    return 3.0 * f if backward else f
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as fh:
+            d = json.load(fh)
+        return dict(tflops=float(d["bf16_tflops_sustained"]), burst=float(d["bf16_tflops"]),
+                    hbm=float(d["hbm_gbs"]), source="measured")
+    except Exception:
+        return dict(tflops=1400.0, burst=1590.0, hbm=6650.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region (reading only)."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc = index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        sm, mx, reasons = [], [], set()
+        for line in out.splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        busy = [s for s in sm if s > 0.5 * max(sm)] or sm
+        return {"sm_mhz": statistics.median(busy), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_inputs(wl, rank, world, dev):
+    """Seeded synthetic inputs: per-step tensors in pinned host memory, parameters on the device."""
+    T, H, I, E, K = wl["T"], wl["H"], wl["I"], wl["E"], wl["K"]
+    El = E // world
+    g = torch.Generator(device=dev).manual_seed(1000 * 0 + rank)           # seed 0, offset by rank
+    x = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    if wl["router"] == "linear":
+        w_r = torch.randn(E, H, generator=g, device=dev) * 0.02
+        logits = x.float() @ w_r.T
+    else:
+        logits = torch.rand(T, E, generator=g, device=dev)
+    vals, idx = torch.topk(torch.softmax(logits, dim=-1), K, dim=-1)
+    rw = (vals / vals.sum(-1, keepdim=True)).float()
+    d_out = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
+    mk = lambda *s, fan: (torch.randn(*s, generator=g, device=dev) * fan ** -0.5).to(torch.bfloat16)  # noqa: E731
+    params = [mk(I, H, fan=H), mk(I, H, fan=H), mk(H, I, fan=I),
+              mk(El, I, H, fan=H), mk(El, I, H, fan=H), mk(El, H, I, fan=I)]
+    host = {k: v.cpu().pin_memory() for k, v in dict(x=x, topk=idx.to(torch.int64), rw=rw, d_out=d_out).items()}
+    return host, params
+
+
+def run_ours(args, rank, world, local_rank):
+    import mok
+    F, L = mok.functional, mok._lib
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if not dist.is_initialized():
+        if world > 1:
+            dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+        else:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29560")
+            dist.init_process_group("gloo", rank=0, world_size=1)
+    name = args.workload if args.workload != "auto" else ("C2" if world == 1 else "C3")
+    wl = WORKLOADS[name]
+    T, H, I, E, K = wl["T"], wl["H"], wl["I"], wl["E"], wl["K"]
+    El = E // world
+    cfg = F.MoKConfig(minibatch_size=wl["minibatch"], macrobatch_size=wl["macrobatch"],
+                      schedule_capacity_multiplier=wl["multiplier"])
+    ws = F.get_workspace(cfg, dist.group.WORLD, device=dev, num_local_tokens=T, hidden_size=H, topk=K)
+    host, params = make_inputs(wl, rank, world, dev)
+    dev_in = {k: v.to(dev) for k, v in host.items()}
+    out_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    dx_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    drw_host = torch.empty(T, K, dtype=torch.float32).pin_memory()
+
+    def step(inp):
+        sched = F.build_schedule(ws, cfg, inp["topk"], num_local_experts=El)
+        out, ctx = F.forward(cfg, ws, sched, inp["x"], inp["rw"], *params)
+        if wl["backward"]:
+            grads = F.backward(cfg, ws, sched, ctx, inp["d_out"], inp["x"], inp["rw"], *params)
+            return out, grads
+        return out, None
+
+    def step_e2e():
+        inp = {k: v.to(dev, non_blocking=True) for k, v in host.items() if k != "d_out" or wl["backward"]}
+        out, grads = step(inp)
+        out_host.copy_(out, non_blocking=True)
+        if grads is not None:
+            dx_host.copy_(grads[0], non_blocking=True)
+            drw_host.copy_(grads[1], non_blocking=True)
+        torch.cuda.current_stream().synchronize()     # the caller reads the result
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            fn()
+        b.record()
+        barrier()
+        ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return ms.item() / steps
+
+    for _ in range(max(args.warmup, 3)):
+        step(dev_in)
+    torch.cuda.synchronize()
+    mok.raise_for_status(dev)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    L.mok_profile_enable(1)
+    L.profile_collect()
+    launches0 = L.mok_launch_count()
+    ms_step = timed(lambda: step(dev_in), args.steps)
+    launches = L.mok_launch_count() - launches0
+    prof = L.profile_collect()
+    L.mok_profile_enable(0)
+    clocks = sampler.stop() if rank == 0 else None
+
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    mok.raise_for_status(dev)
+
+    flops = layer_flops(T, K, H, I, wl["backward"])
+    peaks = measured_peaks()
+    dom = "gemm_gate_up_swiglu_routed"
+    dom_ms, dom_cnt = prof.get(dom, (0.0, 0))
+    dom_ms_step = dom_ms / args.steps if dom_cnt else None
+    dom_flops = 4.0 * T * K * H * I      # gate + up GEMMs over the T*K routed rows (padding not counted)
+    achieved = dom_flops / (dom_ms_step * 1e-3) / 1e12 if dom_ms_step else None
+    if rank != 0:
+        return
+    h2d = sum(v.numel() * v.element_size() for k, v in host.items() if k != "d_out" or wl["backward"])
+    d2h = out_host.numel() * 2 + ((dx_host.numel() * 2 + drw_host.numel() * 4) if wl["backward"] else 0)
+    line = {
+        "metric": METRIC, "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": UNIT,
+        "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{name}: {wl['desc']}", "ep_size": world, "tokens_per_rank": T, "hidden": H,
+                   "intermediate": I, "experts": E, "topk": K, "minibatch_size": wl["minibatch"],
+                   "macrobatch_size": wl["macrobatch"], "pass": "fwd+bwd" if wl["backward"] else "fwd (incl. build_schedule)",
+                   "l2": "inputs larger than L2 (no flush needed)", "per_gpu_tflops": flops / (ms_step * 1e-3) / 1e12,
+                   "pct_of_measured_bf16_peak": 100.0 * flops / (ms_step * 1e-3) / 1e12 / peaks["tflops"]},
+        "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
+                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+        "gpu_launches": int(launches),
+        "clocks": clocks,
+        "roofline": {"kernel": dom, "bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
+                     "frac": (achieved / peaks["tflops"]) if achieved else None, "traffic": NCU_TRAFFIC_BYTES.get(name),
+                     "peak_source": f"{peaks['source']}: bf16_tflops_sustained (kernel timed inside a long step); burst {peaks['burst']}",
+                     "launches_per_step": dom_cnt / args.steps if dom_cnt else 0,
+                     "ms_per_step": dom_ms_step},
+        "kernel_ms_per_step": {k: v[0] / args.steps for k, v in sorted(prof.items())},
+    }
+    if world == 1:
+        line["cpu_baseline"] = cpu_baseline(name, steps=1)
+    print(json.dumps(line), flush=True)
+
+
+def cpu_baseline(name, steps=1, sample_tokens=None):
+    """The CPU oracle on a bounded sample of the workload: same H, I, E, K and router law, fewer
+    tokens per rank, single process, all host threads."""
+    from oracle import mok_oracle as O
+    wl = WORKLOADS[name]
+    W = 1
+    T = sample_tokens or (4096 if not wl["backward"] else 1024)
+    cfgs = dict(T=T, H=wl["H"], I=wl["I"], E=wl["E"], W=W, K=wl["K"], seed=0, router=wl["router"],
+                with_grad=wl["backward"])
+    ranks = [O.make_rank_inputs(r, **cfgs) for r in range(W)]
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        O.layer_forward_backward(ranks, device_rounding=True, backward=wl["backward"])
+        times.append(time.perf_counter() - t0)
+    sec = statistics.median(times)
+    fl = W * layer_flops(T, wl["K"], wl["H"], wl["I"], wl["backward"])
+    return {"value": fl / sec / 1e12, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"{T} tokens (of {wl['T']}) on one virtual rank, all {wl['E']} experts local, "
+                      f"{'fwd+bwd' if wl['backward'] else 'fwd'}, {sec:.2f} s per step", "seconds_per_step": sec}
+
+
+def run_reference(args, rank, world):
+    """The reference arm: the reference's CPU implementation of the path (its pure-PyTorch test
+    oracle, restated in oracle/) on the host cores, on a bounded sample per step."""
+    if rank != 0:
+        return
+    name = args.workload if args.workload != "auto" else ("C2" if world == 1 else "C3")
+    wl = WORKLOADS[name]
+    steps = max(1, min(args.steps, 3))
+    base = cpu_baseline(name, steps=steps)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": world,
+        "steps": steps, "warmup": 0, "ms_per_step": base["seconds_per_step"] * 1e3, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": f"{name}: {wl['desc']}", "note": "CPU port of the reference's PyTorch oracle; "
+                   "the reference's own sm_100 build needs ThunderKittens and CUDA 13, neither available offline"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="auto", choices=["auto", "C2", "C3"])
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("--gpus N with N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    try:
+        run_ours(args, rank, world, local_rank)
+    finally:
+        if dist.is_initialized():
+            try:
+                import mok
+                mok.functional.clear_workspace_cache()
+            except Exception:
+                pass
+            dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -148,6 +148,18 @@ typedef struct mok_bwd_bf16_args {
 } mok_bwd_bf16_args;
 int mok_bwd_bf16(const mok_bwd_bf16_args* args, void* stream);
 
+/* Launch accounting for benchmarks.  mok_launch_count(): kernels launched by this library since it
+ * was loaded.  With mok_profile_enable(1) every launch is bracketed by CUDA events on its stream;
+ * mok_profile_collect() waits for them and adds device milliseconds and launch counts per slot
+ * (slot names from mok_profile_slot_name) into arrays of mok_profile_num_slots() entries.
+ * No counterpart in the reference (its benchmarks time whole passes only,
+ * benchmarks/utils.py:66-110). */
+long long mok_launch_count(void);
+int mok_profile_enable(int on);
+int mok_profile_num_slots(void);
+const char* mok_profile_slot_name(int slot);
+int mok_profile_collect(double* ms_per_slot, long long* launches_per_slot);
+
 /* Building block exposed for tests and tuning: C[M,N] (bf16) = A * B with fp32 accumulation on
  * tcgen05.  a_mn_major / b_mn_major select the memory layout of the operands:
  *   A: 0 = [M, K] row-major (K-major), 1 = [K, M] row-major (M-major)

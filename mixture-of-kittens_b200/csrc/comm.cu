@@ -3,6 +3,7 @@
 // two HBM-bound epilogues.  All peer traffic is plain unicast ld/st on peer-mapped addresses;
 // there is no cluster multicast and no library collective on this path.
 #include "comm.cuh"
+#include "profile.cuh"
 
 namespace mok {
 namespace {
@@ -189,12 +190,14 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(RowMoveParams p) {
 }
 
 int launch_dispatch_rows(const RowMoveParams& p, bool scale, int num_blocks, cudaStream_t stream) {
+    ProfScope prof(kSlotDispatch, stream);
     if (scale) dispatch_rows_kernel<true><<<num_blocks, 256, 0, stream>>>(p);
     else dispatch_rows_kernel<false><<<num_blocks, 256, 0, stream>>>(p);
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
 }
 int launch_combine_rows(const RowMoveParams& p, int num_blocks, cudaStream_t stream) {
+    ProfScope prof(kSlotCombine, stream);
     combine_rows_kernel<<<num_blocks, 256, 0, stream>>>(p);
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
@@ -215,6 +218,7 @@ extern "C" int mok_all_gather_top_experts(const int32_t* top_experts, int64_t nu
     }
     const int64_t n_vec = numel / 4;
     const int blocks = static_cast<int>(std::min<int64_t>((n_vec + 255) / 256, 296));
+    ProfScope prof(kSlotAllGather, static_cast<cudaStream_t>(stream));
     all_gather_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const int4*>(top_experts), n_vec,
                                                                              numel, peers, ep_size, rank);
     MOK_CUDA_CHECK(cudaGetLastError());
@@ -230,6 +234,7 @@ extern "C" int mok_barrier_all(uint32_t* local_counter, const uint64_t* peer_cou
         if (!peer_counter_ptrs[i]) return MOK_ERR_INVALID;
         peers.p[i] = reinterpret_cast<void*>(peer_counter_ptrs[i]);
     }
+    ProfScope prof(kSlotBarrier, static_cast<cudaStream_t>(stream));
     barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(local_counter, peers, ep_size, target, status,
                                                                     timeout_ns ? timeout_ns : kWaitLimitNs);
     MOK_CUDA_CHECK(cudaGetLastError());
@@ -245,6 +250,7 @@ extern "C" int mok_fwd_epilogue(const void* y_shared, const void* combine_buffer
     if (!y_shared || !combine_buffer || !topk_weights || !output) return MOK_ERR_INVALID;
     if (num_local_tokens <= 0 || hidden <= 0 || hidden % 8 || topk <= 0) return MOK_ERR_INVALID;
     const int vpr = hidden / 8;
+    ProfScope prof(kSlotEpilogue, static_cast<cudaStream_t>(stream));
     epilogue_kernel<true><<<epilogue_grid(static_cast<int64_t>(num_local_tokens) * vpr), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(y_shared), static_cast<const uint4*>(combine_buffer), topk_weights,
         static_cast<uint4*>(output), num_local_tokens, vpr, topk);
@@ -257,6 +263,7 @@ extern "C" int mok_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_b
     if (!d_x_shared || !d_x_routed_buffer || !d_x) return MOK_ERR_INVALID;
     if (num_local_tokens <= 0 || hidden <= 0 || hidden % 8 || topk <= 0) return MOK_ERR_INVALID;
     const int vpr = hidden / 8;
+    ProfScope prof(kSlotEpilogue, static_cast<cudaStream_t>(stream));
     epilogue_kernel<false><<<epilogue_grid(static_cast<int64_t>(num_local_tokens) * vpr), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(d_x_shared), static_cast<const uint4*>(d_x_routed_buffer), nullptr,
         static_cast<uint4*>(d_x), num_local_tokens, vpr, topk);

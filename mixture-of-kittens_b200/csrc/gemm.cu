@@ -70,7 +70,7 @@ int launch_inst(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap&
 }  // namespace
 
 int launch_grouped_gemm(int a_major, int b_major, int epi, bool wgrad, const GemmOperands& ops, const GemmParams& p,
-                        int max_tiles, int max_ctas, cudaStream_t stream) {
+                        int max_tiles, int max_ctas, int prof_slot, cudaStream_t stream) {
     if (max_tiles <= 0) return MOK_OK;
     CUtensorMap a0, b0, a1, b1;
     // A: K-major box {64 K, 128 rows}; M-major box {64 M, 64 K-rows}
@@ -85,6 +85,7 @@ int launch_grouped_gemm(int a_major, int b_major, int epi, bool wgrad, const Gem
     int ctas = device_sm_count();
     if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
     const int grid = max_tiles < ctas ? max_tiles : ctas;
+    ProfScope prof(prof_slot, stream);
 
     if (!wgrad && a_major == kMajorK && b_major == kMajorK && epi == kEpiStore)
         return launch_inst<kMajorK, kMajorK, kEpiStore, false>(a0, b0, a1, b1, p, grid, stream);
@@ -136,5 +137,5 @@ extern "C" int mok_gemm_bf16(const void* a, const void* b, void* c, int m, int n
     }
     const int tiles = (m / kBlockM) * (n / kBlockN);
     return launch_grouped_gemm(a_mn_major ? kMajorMN : kMajorK, b_mn_major ? kMajorMN : kMajorK, kEpiStore, wgrad, ops, p,
-                               tiles, 0, static_cast<cudaStream_t>(stream));
+                               tiles, 0, kSlotGemmTest, static_cast<cudaStream_t>(stream));
 }

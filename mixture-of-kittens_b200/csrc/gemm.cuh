@@ -19,6 +19,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "profile.cuh"
 
 namespace mok {
 
@@ -385,6 +386,6 @@ struct GemmOperands {
 };
 // a_major/b_major/epi/wgrad select the instantiation; `max_ctas` caps the grid (0 = all SMs)
 int launch_grouped_gemm(int a_major, int b_major, int epi, bool wgrad, const GemmOperands& ops, const GemmParams& p,
-                        int max_tiles, int max_ctas, cudaStream_t stream);
+                        int max_tiles, int max_ctas, int prof_slot, cudaStream_t stream);
 
 }  // namespace mok

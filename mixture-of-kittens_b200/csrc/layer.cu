@@ -78,7 +78,8 @@ int run_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int off, 
     o.a0 = a; o.b0 = wg; o.b1 = wu;
     o.a_inner = d.H; o.a_outer = a_rows;
     o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.I;
-    return launch_grouped_gemm(kMajorK, kMajorK, kEpiSwigluFwd, false, o, p, (limit / kBlockM) * p.n_tiles, 0, s);
+    return launch_grouped_gemm(kMajorK, kMajorK, kEpiSwigluFwd, false, o, p, (limit / kBlockM) * p.n_tiles, 0,
+                               routed ? kSlotGateUpRouted : kSlotGateUpShared, s);
 }
 
 // down GEMM: A = hidden [rows, I] K-major, B = Wd [E*H, I] K-major
@@ -94,7 +95,8 @@ int run_down(const mok_layer_common& c, const Dims& d, bool routed, int off, int
     o.a0 = hidden; o.b0 = wd;
     o.a_inner = d.I; o.a_outer = a_rows;
     o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.H;
-    return launch_grouped_gemm(kMajorK, kMajorK, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0, s);
+    return launch_grouped_gemm(kMajorK, kMajorK, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0,
+                               routed ? kSlotDownRouted : kSlotDownShared, s);
 }
 
 // d_hidden = d_y @ Wd (B is [E*H, I] read N-major), fused SwiGLU backward
@@ -117,7 +119,8 @@ int run_dgrad_down(const mok_layer_common& c, const Dims& d, bool routed, int of
     o.a0 = d_y; o.b0 = wd;
     o.a_inner = d.H; o.a_outer = a_rows;
     o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.H;
-    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiSwigluBwd, false, o, p, (limit / kBlockM) * p.n_tiles, 0, s);
+    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiSwigluBwd, false, o, p, (limit / kBlockM) * p.n_tiles, 0,
+                               routed ? kSlotDgradDownRouted : kSlotDgradDownShared, s);
 }
 
 // d_x = d_gate @ Wg + d_up @ Wu in one accumulator (B = [E*I, H] read N-major)
@@ -134,7 +137,8 @@ int run_dgrad_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int
     o.a0 = d_gate; o.a1 = d_up; o.b0 = wg; o.b1 = wu;
     o.a_inner = d.I; o.a_outer = a_rows;
     o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.I;
-    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0, s);
+    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0,
+                               routed ? kSlotDgradGateUpRouted : kSlotDgradGateUpShared, s);
 }
 
 // dW[e] [m, n] = A[rows_e, m]^T @ B[rows_e, n]; both operands are read MN-major straight from the
@@ -153,7 +157,8 @@ int run_wgrad(const mok_layer_common& c, bool routed, int off, int limit, const 
     o.a_inner = m; o.a_outer = rows;
     o.b_inner = n; o.b_outer = rows;
     const int experts = routed ? c.num_local_experts : 1;
-    return launch_grouped_gemm(kMajorMN, kMajorMN, kEpiStore, true, o, p, experts * p.m_tiles_w * p.n_tiles, 0, s);
+    return launch_grouped_gemm(kMajorMN, kMajorMN, kEpiStore, true, o, p, experts * p.m_tiles_w * p.n_tiles, 0,
+                               routed ? kSlotWgradRouted : kSlotWgradShared, s);
 }
 
 RowMoveParams row_move(const mok_layer_common& c, const Dims& d, int off, int limit, void* local) {

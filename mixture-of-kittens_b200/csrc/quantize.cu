@@ -5,6 +5,7 @@
 //   q = cvt.rn.satfinite.e4m3(x * 2^(127-e)).
 // HBM-bound: reads 2 B/element once, writes 1 B/element per requested layout (+1/32 for scales).
 #include "common.cuh"
+#include "profile.cuh"
 
 namespace mok {
 
@@ -124,6 +125,7 @@ extern "C" int mok_mxfp8_quantize(const void* x_bf16, int num_matrices, int rows
     const auto* x = static_cast<const __nv_bfloat16*>(x_bf16);
     auto* q = static_cast<uint8_t*>(x_fp8); auto* sc = static_cast<uint8_t*>(x_sc);
     auto* qt = static_cast<uint8_t*>(x_fp8_t); auto* sct = static_cast<uint8_t*>(x_sc_t);
+    ProfScope prof(kSlotQuantize, s);
     if (normal && transposed) mxfp8_quantize_kernel<true, true><<<grid, 256, 0, s>>>(x, rows, cols, q, sc, qt, sct);
     else if (normal) mxfp8_quantize_kernel<true, false><<<grid, 256, 0, s>>>(x, rows, cols, q, sc, qt, sct);
     else mxfp8_quantize_kernel<false, true><<<grid, 256, 0, s>>>(x, rows, cols, q, sc, qt, sct);

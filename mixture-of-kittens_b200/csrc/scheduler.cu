@@ -13,6 +13,7 @@
 //           order, ranks equal experts inside the warp with match.any, and writes the slots.
 // Algorithmic traffic: 2 * W*T*K*4 B of route reads + 2 * capacity * 4 B of table writes.
 #include "common.cuh"
+#include "profile.cuh"
 
 namespace mok {
 namespace {
@@ -237,6 +238,7 @@ int launch_schedule(const int32_t* topk_all, int ep_size, int num_local_tokens, 
     const size_t smem_place = (static_cast<size_t>(p.El) * p.W + p.El + static_cast<size_t>(kWarpsPerBlock) * p.El) * sizeof(int);
     MOK_CUDA_CHECK(cudaFuncSetAttribute(sched_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_count)));
     MOK_CUDA_CHECK(cudaFuncSetAttribute(sched_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_place)));
+    ProfScope prof(kSlotScheduler, stream, 3);
     sched_count_kernel<<<chunk_blocks, kBlockThreads, smem_count, stream>>>(p);
     const int pair_blocks = (p.El * p.W + kWarpsPerBlock - 1) / kWarpsPerBlock;
     sched_scan_kernel<<<pair_blocks, kBlockThreads, 0, stream>>>(p);

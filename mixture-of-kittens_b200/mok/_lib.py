@@ -104,6 +104,11 @@ mok_fwd_epilogue = _sig("mok_fwd_epilogue", C.c_int, [vp, vp, vp, vp, C.c_int, C
 mok_bwd_epilogue = _sig("mok_bwd_epilogue", C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp])
 mok_fwd_bf16 = _sig("mok_fwd_bf16", C.c_int, [C.POINTER(FwdBf16Args), vp])
 mok_bwd_bf16 = _sig("mok_bwd_bf16", C.c_int, [C.POINTER(BwdBf16Args), vp])
+mok_launch_count = _sig("mok_launch_count", C.c_longlong, [])
+mok_profile_enable = _sig("mok_profile_enable", C.c_int, [C.c_int])
+mok_profile_num_slots = _sig("mok_profile_num_slots", C.c_int, [])
+mok_profile_slot_name = _sig("mok_profile_slot_name", C.c_char_p, [C.c_int])
+mok_profile_collect = _sig("mok_profile_collect", C.c_int, [C.POINTER(C.c_double), C.POINTER(C.c_longlong)])
 mok_gemm_bf16 = _sig("mok_gemm_bf16", C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp])
 
 
@@ -173,3 +178,12 @@ def unregister_all_gather_peers(local_ptr: int) -> None:
 
 def all_gather_peers(local_ptr: int) -> list[int] | None:
     return _ALL_GATHER_PEERS.get(int(local_ptr))
+
+
+def profile_collect() -> dict[str, tuple[float, int]]:
+    """Device milliseconds and launch counts per slot recorded since the last call (synchronises)."""
+    n = mok_profile_num_slots()
+    ms = (C.c_double * n)()
+    cnt = (C.c_longlong * n)()
+    check(mok_profile_collect(ms, cnt), "profile_collect")
+    return {mok_profile_slot_name(i).decode(): (ms[i], cnt[i]) for i in range(n) if cnt[i]}

@@ -1,0 +1,130 @@
+"""GPU parity tests of the whole layer on one rank (EP=1) through mok.functional, against the CPU
+oracle: forward outputs, all eight gradients, saved activations, macrobatch replay, SwiGLU clamp,
+run-to-run determinism, and a full-size forward checked through sampled tokens."""
+import pytest
+import torch
+
+from oracle import mok_oracle as O
+from tests.helpers import BF16_REL_L2, rel_l2
+
+pytestmark = pytest.mark.gpu
+
+GRAD_NAMES = ("d_x", "d_router_weights", "d_w_routed_gate", "d_w_routed_up", "d_w_routed_down",
+              "d_w_shared_gate", "d_w_shared_up", "d_w_shared_down")
+
+
+def run_layer(dev, group, inp: O.RankInputs, *, limit=None, macrobatch=131072, minibatch=256, multiplier=2.0,
+              backward=True):
+    import mok
+    F = mok.functional
+    T, H = inp.x.shape
+    K = inp.topk_experts.shape[1]
+    El = inp.w_routed_gate.shape[0]
+    mok.last_status(dev, clear=True)
+    cfg = F.MoKConfig(macrobatch_size=macrobatch, minibatch_size=minibatch, schedule_capacity_multiplier=multiplier,
+                      all_gather_top_experts_chunk_bytes=16)
+    ws = F.get_workspace(cfg, group, device=dev, num_local_tokens=T, hidden_size=H, topk=K)
+    d = lambda t: t.to(dev)  # noqa: E731
+    x, rw = d(inp.x), d(inp.router_weights)
+    weights = [d(w) for w in (inp.w_shared_gate, inp.w_shared_up, inp.w_shared_down, inp.w_routed_gate,
+                              inp.w_routed_up, inp.w_routed_down)]
+    sched = F.build_schedule(ws, cfg, d(inp.topk_experts), num_local_experts=El)
+    out, ctx = F.forward(cfg, ws, sched, x, rw, *weights, swiglu_limit=limit)
+    res = {"output": out, "ctx": ctx, "schedule": sched}
+    if backward:
+        grads = F.backward(cfg, ws, sched, ctx, d(inp.d_output), x, rw, *weights, swiglu_limit=limit)
+        res.update(dict(zip(GRAD_NAMES, grads)))
+    torch.cuda.synchronize()
+    assert mok.last_status(dev)[0] == 0, mok.last_status(dev)
+    return res
+
+
+SMALL = dict(T=512, H=256, I=256, E=4, W=1, K=2)
+
+
+@pytest.mark.parametrize("limit", [None, 1.0])
+def test_forward_backward_small(cuda_device, single_rank_group, limit):
+    inp = O.make_rank_inputs(0, seed=21, **SMALL)
+    ref = O.layer_forward_backward([inp], swiglu_limit=limit, device_rounding=True)[0]
+    got = run_layer(cuda_device, single_rank_group, inp, limit=limit)
+    assert rel_l2(ref["output"].float(), got["output"].float()) < BF16_REL_L2
+    for name in GRAD_NAMES:
+        assert rel_l2(ref[name].float(), got[name].float()) < BF16_REL_L2, name
+    # schedule tables are exact
+    for name in ("peer_rank", "peer_token_idx", "num_tokens", "tokens_per_expert"):
+        cap = got["schedule"].peer_rank.numel()
+        r = O.schedule_tables(inp.topk_experts.numpy().astype("int32")[None], SMALL["E"], cap, 0)
+        g = getattr(got["schedule"], name).cpu().numpy()
+        assert (dict(zip(("peer_rank", "peer_token_idx", "num_tokens", "tokens_per_expert"), r))[name] == g).all()
+
+
+@pytest.mark.parametrize("cfg", [dict(T=1024, H=512, I=768, E=8, W=1, K=4), dict(T=768, H=1024, I=256, E=3, W=1, K=3),
+                                  dict(T=512, H=256, I=512, E=16, W=1, K=1)])
+def test_forward_backward_shapes(cuda_device, single_rank_group, cfg):
+    inp = O.make_rank_inputs(0, seed=5, **cfg)
+    ref = O.layer_forward_backward([inp], device_rounding=True)[0]
+    got = run_layer(cuda_device, single_rank_group, inp, multiplier=8.0)   # capacity for E * 256 padded rows
+    assert rel_l2(ref["output"].float(), got["output"].float()) < BF16_REL_L2
+    for name in GRAD_NAMES:
+        assert rel_l2(ref[name].float(), got[name].float()) < BF16_REL_L2, name
+
+
+def test_multiple_macrobatches_replay(cuda_device, single_rank_group):
+    """A macrobatch smaller than the schedule forces several windows and the replay path; results
+    must agree with the single-window run up to the bf16 accumulation of weight gradients."""
+    cfg = dict(T=1024, H=256, I=256, E=4, W=1, K=2)
+    inp = O.make_rank_inputs(0, seed=8, **cfg)
+    ref = O.layer_forward_backward([inp], device_rounding=True)[0]
+    one = run_layer(cuda_device, single_rank_group, inp, macrobatch=131072)
+    many = run_layer(cuda_device, single_rank_group, inp, macrobatch=512, minibatch=256)
+    assert torch.equal(one["output"], many["output"])
+    assert torch.equal(one["d_x"], many["d_x"])
+    assert torch.equal(one["d_router_weights"], many["d_router_weights"])
+    for name in GRAD_NAMES:
+        assert rel_l2(ref[name].float(), many[name].float()) < BF16_REL_L2, name
+
+
+def test_two_runs_are_bit_identical(cuda_device, single_rank_group):
+    cfg = dict(T=1024, H=512, I=512, E=8, W=1, K=4)
+    inp = O.make_rank_inputs(0, seed=13, **cfg)
+    a = run_layer(cuda_device, single_rank_group, inp)
+    b = run_layer(cuda_device, single_rank_group, inp)
+    assert torch.equal(a["output"], b["output"])
+    for name in GRAD_NAMES:
+        assert torch.equal(a[name], b[name]), name
+
+
+def test_saved_activations_match_oracle(cuda_device, single_rank_group):
+    """x_routed is an exact gather; padding rows are zero."""
+    inp = O.make_rank_inputs(0, seed=21, **SMALL)
+    got = run_layer(cuda_device, single_rank_group, inp, backward=False)
+    sched, ctx = got["schedule"], got["ctx"]
+    n = int(sched.num_tokens.item())
+    pr, pt = sched.peer_rank.cpu()[:n], sched.peer_token_idx.cpu()[:n]
+    expect = torch.zeros(n, SMALL["H"], dtype=torch.bfloat16)
+    valid = pr >= 0
+    expect[valid] = inp.x[(pt[valid] // SMALL["K"]).long()]
+    assert torch.equal(expect, ctx.x_routed.cpu()[:n])
+
+
+def test_full_size_forward_sampled(cuda_device, single_rank_group):
+    """BASELINE config 2 shape (T=16384, H=2048, 128 experts, top-8, I=768): the oracle is too
+    slow for every token, so 48 sampled tokens are recomputed in fp32 on the CPU oracle path."""
+    cfg = dict(T=16384, H=2048, I=768, E=128, W=1, K=8)
+    inp = O.make_rank_inputs(0, seed=0, with_grad=False, **cfg)
+    got = run_layer(cuda_device, single_rank_group, inp, macrobatch=262144, minibatch=4096, backward=False)
+    out = got["output"].cpu().float()
+    assert torch.isfinite(out).all()
+    idx = torch.arange(0, cfg["T"], cfg["T"] // 48)[:48]
+    x = inp.x[idx].float()
+    rd = lambda t: t.to(torch.bfloat16).float()  # noqa: E731
+    g, u = rd(x @ inp.w_shared_gate.float().T), rd(x @ inp.w_shared_up.float().T)
+    acc = rd(rd(O.swiglu_fwd(g, u, None)) @ inp.w_shared_down.float().T)
+    for k in range(cfg["K"]):
+        e = inp.topk_experts[idx, k]
+        ge = rd(torch.einsum("th,tih->ti", x, inp.w_routed_gate[e].float()))
+        ue = rd(torch.einsum("th,tih->ti", x, inp.w_routed_up[e].float()))
+        he = rd(O.swiglu_fwd(ge, ue, None))
+        ye = rd(torch.einsum("ti,thi->th", he, inp.w_routed_down[e].float()))
+        acc = acc + ye * inp.router_weights[idx, k:k + 1]
+    assert rel_l2(rd(acc), out[idx]) < BF16_REL_L2
