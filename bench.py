@@ -149,7 +149,10 @@ def run_ours(args, rank, world, local_rank):
             os.environ.setdefault("MASTER_PORT", "29560")
             dist.init_process_group("gloo", rank=0, world_size=1)
     name = args.workload if args.workload != "auto" else ("C2" if world == 1 else "C3")
-    wl = WORKLOADS[name]
+    wl = dict(WORKLOADS[name])
+    if args.tokens:                      # smaller copy of the workload (profiler captures); never a bench value
+        wl["T"] = args.tokens
+        wl["desc"] += f" [reduced to {args.tokens} tokens per rank]"
     T, H, I, E, K = wl["T"], wl["H"], wl["I"], wl["E"], wl["K"]
     El = E // world
     cfg = F.MoKConfig(minibatch_size=wl["minibatch"], macrobatch_size=wl["macrobatch"],
@@ -196,14 +199,13 @@ def run_ours(args, rank, world, local_rank):
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
         return ms.item() / steps
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(max(args.warmup, 3)):
         step(dev_in)
     torch.cuda.synchronize()
     mok.raise_for_status(dev)
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     L.mok_profile_enable(1)
     L.profile_collect()
     launches0 = L.mok_launch_count()
@@ -249,7 +251,7 @@ def run_ours(args, rank, world, local_rank):
                      "ms_per_step": dom_ms_step},
         "kernel_ms_per_step": {k: v[0] / args.steps for k, v in sorted(prof.items())},
     }
-    if world == 1:
+    if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(name, steps=1)
     print(json.dumps(line), flush=True)
 
@@ -300,10 +302,12 @@ def run_reference(args, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="auto", choices=["auto", "C2", "C3"])
+    ap.add_argument("--tokens", type=int, default=0, help="override tokens per rank (profiling a reduced case)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

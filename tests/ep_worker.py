@@ -1,0 +1,91 @@
+"""Multi-rank parity worker (one process per GPU, launched by torch.distributed.run).
+
+Every rank rebuilds the seeded inputs of ALL ranks on the CPU, runs the oracle over the W virtual
+ranks, then runs the real layer (build_schedule -> forward -> backward through mok.functional over
+symmetric memory) and compares its own rank's results with the oracle's.  Exit code 0 = parity.
+"""
+import json
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+for p in (ROOT, os.path.join(ROOT, "mixture-of-kittens_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+GRADS = ("d_x", "d_router_weights", "d_w_routed_gate", "d_w_routed_up", "d_w_routed_down",
+         "d_w_shared_gate", "d_w_shared_up", "d_w_shared_down")
+
+
+def rel(a, b):
+    a, b = a.double().cpu(), b.double().cpu()
+    n = a.norm().item()
+    return (a - b).norm().item() / (n if n > 0 else 1.0)
+
+
+def main():
+    import mok
+    from oracle import mok_oracle as O
+    rank, world, local = (int(os.environ[k]) for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK"))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    F = mok.functional
+    cases = [dict(T=512, H=256, I=256, E=2 * world, K=2, limit=None, macro=131072, zipf=None),
+             dict(T=1024, H=512, I=512, E=4 * world, K=4, limit=1.0, macro=131072, zipf=None),
+             dict(T=512, H=256, I=256, E=2 * world, K=2, limit=None, macro=512, zipf=1.2)]
+    worst, failures = 0.0, []
+    for ci, c in enumerate(cases):
+        shape = dict(T=c["T"], H=c["H"], I=c["I"], E=c["E"], W=world, K=c["K"], seed=40 + ci, zipf_s=c["zipf"])
+        ranks = [O.make_rank_inputs(r, **shape) for r in range(world)]
+        mult = float(world)                       # capacity = T*K*W: nothing can overflow
+        cap = c["T"] * c["K"] * max(2, world)
+        ref = O.layer_forward_backward(ranks, swiglu_limit=c["limit"], device_rounding=True, capacity=cap)[rank]
+        cfg = F.MoKConfig(minibatch_size=256, macrobatch_size=c["macro"], schedule_capacity_multiplier=mult,
+                          all_gather_top_experts_chunk_bytes=16)
+        ws = F.get_workspace(cfg, dist.group.WORLD, device=dev, num_local_tokens=c["T"], hidden_size=c["H"], topk=c["K"])
+        me = ranks[rank]
+        d = lambda t: t.to(dev)  # noqa: E731
+        w = [d(t) for t in (me.w_shared_gate, me.w_shared_up, me.w_shared_down, me.w_routed_gate, me.w_routed_up,
+                            me.w_routed_down)]
+        x, rw = d(me.x), d(me.router_weights)
+        outs = []
+        for rep in range(2):                      # second pass: bit-identical
+            sched = F.build_schedule(ws, cfg, d(me.topk_experts), num_local_experts=c["E"] // world)
+            out, ctx = F.forward(cfg, ws, sched, x, rw, *w, swiglu_limit=c["limit"])
+            grads = F.backward(cfg, ws, sched, ctx, d(me.d_output), x, rw, *w, swiglu_limit=c["limit"])
+            torch.cuda.synchronize()
+            outs.append((out, grads))
+        code = mok.last_status(dev)[0]
+        if code != 0:
+            failures.append(f"case {ci}: status {mok.last_status(dev)}")
+        for name, r_, g_ in zip(("peer_rank", "peer_token_idx", "num_tokens", "tokens_per_expert"),
+                                (ref["peer_rank"], ref["peer_token_idx"], ref["num_tokens"], ref["tokens_per_expert"]),
+                                (sched.peer_rank, sched.peer_token_idx, sched.num_tokens, sched.tokens_per_expert)):
+            if not np.array_equal(r_, g_.cpu().numpy()):
+                failures.append(f"case {ci}: schedule table {name} differs")
+        e = rel(ref["output"].float(), outs[1][0].float())
+        worst = max(worst, e)
+        if e > 1e-2:
+            failures.append(f"case {ci}: output rel-L2 {e:.3e}")
+        for name, g_ in zip(GRADS, outs[1][1]):
+            e = rel(ref[name].float(), g_.float())
+            worst = max(worst, e)
+            if e > 1e-2:
+                failures.append(f"case {ci}: {name} rel-L2 {e:.3e}")
+        if not torch.equal(outs[0][0], outs[1][0]) or any(not torch.equal(a, b) for a, b in zip(outs[0][1], outs[1][1])):
+            failures.append(f"case {ci}: two runs differ bitwise")
+    flag = torch.tensor([len(failures)], device=dev)
+    dist.all_reduce(flag)
+    print(json.dumps({"rank": rank, "world": world, "worst_rel_l2": worst, "failures": failures}), flush=True)
+    F.clear_workspace_cache()
+    dist.destroy_process_group()
+    sys.exit(1 if flag.item() else 0)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,23 @@
+"""GPU, 2+ devices: expert-parallel parity.  Spawns one process per GPU with torch.distributed.run
+and checks every rank against the multi-rank CPU oracle (tests/ep_worker.py).  Skipped on a
+single-GPU box; the round's multi-GPU runs call the worker directly."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_expert_parallel_parity(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "ep_worker.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", str(29600 + world), worker]
+    proc = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stdout[-4000:] + proc.stderr[-4000:]
