@@ -30,6 +30,7 @@ extern "C" {
 #define MOK_ERR_INVALID (-1)     /* argument outside the documented domain */
 #define MOK_ERR_CUDA (-2)        /* a CUDA runtime / driver call failed */
 #define MOK_ERR_UNSUPPORTED (-3) /* shape or mode this build does not implement */
+#define MOK_ERR_TOO_LARGE (-4)   /* problem exceeds a fixed, documented size limit of the entry point */
 
 /* device-detected errors (status word code) */
 #define MOK_STATUS_OK 0
@@ -64,6 +65,22 @@ int mok_schedule(const int32_t* topk_all, int ep_size, int num_local_tokens, int
                  int32_t* schedule_peer_rank, int32_t* schedule_peer_token_idx,
                  int32_t* num_tokens, int32_t* tokens_per_expert,
                  void* scratch, size_t scratch_bytes, int32_t* status, void* stream);
+
+/* The same scheduler for callers that cannot allocate device memory (a server with a fixed
+ * memory plan, a latency-critical loop that must not hit cudaMalloc's device synchronisation, a
+ * plug-in host that exposes no allocator): the scratch lives in a fixed 4 MiB __device__ array
+ * inside the library, resident on every GPU that loads it, so only inputs and outputs are passed.
+ * Limit: mok_schedule_scratch_bytes(ep_size, num_local_experts) must not exceed
+ * mok_schedule_static_max_scratch_bytes() (ep_size * num_local_experts <= 4080); larger problems
+ * return MOK_ERR_TOO_LARGE and launch nothing.  The first call on a device looks up the array's
+ * address; make that call outside any stream capture.  Calls on one GPU share the array: calls
+ * that overlap on the GPU race, so issue them one after another.  Results are identical to
+ * mok_schedule.  This entry point has no counterpart in the reference. */
+size_t mok_schedule_static_max_scratch_bytes(void);
+int mok_schedule_static(const int32_t* topk_all, int ep_size, int num_local_tokens, int topk,
+                        int num_local_experts, int schedule_capacity, int rank,
+                        int32_t* schedule_peer_rank, int32_t* schedule_peer_token_idx,
+                        int32_t* num_tokens, int32_t* tokens_per_expert, int32_t* status, void* stream);
 
 /* BF16 [E, M, N] -> MXFP8: E4M3 bytes plus one E8M0 scale per 1x32 block along the last
  * dimension, normal and/or transposed; scales in the [rows/128, cols/128, 32, 16] tcgen05

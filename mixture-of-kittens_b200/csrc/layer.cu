@@ -287,6 +287,7 @@ extern "C" const char* mok_error_string(int code) {
         case MOK_ERR_INVALID: return "invalid argument";
         case MOK_ERR_CUDA: return "CUDA call failed";
         case MOK_ERR_UNSUPPORTED: return "unsupported shape or mode";
+        case MOK_ERR_TOO_LARGE: return "problem exceeds the fixed size limit of this entry point";
         case MOK_STATUS_SCHEDULE_OVERFLOW: return "schedule capacity exceeded";
         case MOK_STATUS_BARRIER_TIMEOUT: return "device barrier timed out";
         case MOK_STATUS_PIPELINE_TIMEOUT: return "kernel pipeline wait timed out";

@@ -263,3 +263,65 @@ extern "C" int mok_schedule(const int32_t* topk_all, int ep_size, int num_local_
                                 schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert,
                                 scratch, status, static_cast<cudaStream_t>(stream));
 }
+
+// ---------------------------------------------------------------------------------------------
+// Scheduler variant for callers that must not allocate device memory.
+//
+// Some hosts of this library run under a fixed memory plan: an inference server that sized its
+// arena at start-up, a real-time loop where cudaMalloc's implicit device synchronisation is not
+// acceptable, or a plug-in boundary that hands out no allocator at all.  Such a caller cannot
+// provide the chunk-histogram scratch mok_schedule() asks for.  This entry point keeps that
+// scratch in a fixed array inside the library image instead, so the call needs nothing beyond the
+// caller's inputs and outputs.
+//
+// The array is a file-scope __device__ object: every GPU that loads the library carries it
+// (kStaticScratchBytes) until the process exits.  In host code its name is only a handle, not a
+// device address, so the address is looked up with cudaGetSymbolAddress once per device, with that
+// device current, on the first call made on that device; later calls reuse the cached address.
+// That first call should therefore be made outside any stream capture.
+//
+// All calls on one GPU share the array.  The kernels overwrite every element they later read, so
+// nothing has to be cleared between calls, but two calls whose kernels overlap on the GPU (two
+// streams, or two threads) race on it: run them one after the other.
+// ---------------------------------------------------------------------------------------------
+namespace mok {
+namespace {
+constexpr size_t kStaticScratchBytes = 4u << 20;   // enough for ep_size * num_local_experts <= 4080
+static __device__ __align__(256) unsigned char g_static_sched_scratch[kStaticScratchBytes];
+void* g_static_scratch_addr[64] = {nullptr};
+
+int static_scratch_for_current_device(void** out) {
+    int dev = -1;
+    MOK_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return MOK_ERR_UNSUPPORTED;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* ptr = nullptr;
+        const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_sched_scratch);
+        if (err != cudaSuccess || ptr == nullptr) return MOK_ERR_CUDA;
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return MOK_OK;
+}
+}  // namespace
+}  // namespace mok
+
+extern "C" size_t mok_schedule_static_max_scratch_bytes(void) { return mok::kStaticScratchBytes; }
+
+extern "C" int mok_schedule_static(const int32_t* topk_all, int ep_size, int num_local_tokens, int topk,
+                                   int num_local_experts, int schedule_capacity, int rank,
+                                   int32_t* schedule_peer_rank, int32_t* schedule_peer_token_idx,
+                                   int32_t* num_tokens, int32_t* tokens_per_expert, int32_t* status, void* stream) {
+    if (!topk_all || !schedule_peer_rank || !schedule_peer_token_idx || !num_tokens || !tokens_per_expert)
+        return MOK_ERR_INVALID;
+    if (ep_size < 1 || ep_size > MOK_MAX_PEERS || rank < 0 || rank >= ep_size) return MOK_ERR_INVALID;
+    if (num_local_tokens <= 0 || topk <= 0 || schedule_capacity <= 0) return MOK_ERR_INVALID;
+    if (num_local_experts < 1 || num_local_experts > MOK_MAX_LOCAL_EXPERTS) return MOK_ERR_INVALID;
+    if (mok_schedule_scratch_bytes(ep_size, num_local_experts) > mok::kStaticScratchBytes) return MOK_ERR_TOO_LARGE;
+    void* scratch = nullptr;
+    const int rc = mok::static_scratch_for_current_device(&scratch);
+    if (rc != MOK_OK) return rc;
+    return mok::launch_schedule(topk_all, ep_size, num_local_tokens, topk, num_local_experts, schedule_capacity, rank,
+                                schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert,
+                                scratch, status, static_cast<cudaStream_t>(stream));
+}

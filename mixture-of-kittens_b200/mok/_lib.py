@@ -99,6 +99,9 @@ mok_barrier_all = _sig("mok_barrier_all", C.c_int, [vp, u64p, C.c_int, vp, vp, C
 mok_schedule_scratch_bytes = _sig("mok_schedule_scratch_bytes", C.c_size_t, [C.c_int, C.c_int])
 mok_schedule = _sig("mok_schedule", C.c_int, [vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
                                               vp, vp, vp, vp, vp, C.c_size_t, vp, vp])
+mok_schedule_static_max_scratch_bytes = _sig("mok_schedule_static_max_scratch_bytes", C.c_size_t, [])
+mok_schedule_static = _sig("mok_schedule_static", C.c_int, [vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int,
+                                                            vp, vp, vp, vp, vp, vp])
 mok_mxfp8_quantize = _sig("mok_mxfp8_quantize", C.c_int, [vp, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp, vp])
 mok_fwd_epilogue = _sig("mok_fwd_epilogue", C.c_int, [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp])
 mok_bwd_epilogue = _sig("mok_bwd_epilogue", C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp])
@@ -121,6 +124,8 @@ def check(rc: int, what: str) -> None:
         raise ValueError(f"{what}: {msg}")
     if rc == -3:
         raise NotImplementedError(f"{what}: {msg}")
+    if rc == -4:
+        raise ValueError(f"{what}: {msg}")
     raise MokNativeError(f"{what}: {msg}")
 
 
