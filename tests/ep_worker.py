@@ -42,7 +42,7 @@ def main():
     for ci, c in enumerate(cases):
         shape = dict(T=c["T"], H=c["H"], I=c["I"], E=c["E"], W=world, K=c["K"], seed=40 + ci, zipf_s=c["zipf"])
         ranks = [O.make_rank_inputs(r, **shape) for r in range(world)]
-        mult = float(world)                       # capacity = T*K*W: nothing can overflow
+        mult = 1.0                                # capacity = T*K*max(2, W): nothing can overflow
         cap = c["T"] * c["K"] * max(2, world)
         ref = O.layer_forward_backward(ranks, swiglu_limit=c["limit"], device_rounding=True, capacity=cap)[rank]
         cfg = F.MoKConfig(minibatch_size=256, macrobatch_size=c["macro"], schedule_capacity_multiplier=mult,
