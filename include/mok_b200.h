@@ -165,6 +165,65 @@ typedef struct mok_bwd_bf16_args {
 } mok_bwd_bf16_args;
 int mok_bwd_bf16(const mok_bwd_bf16_args* args, void* stream);
 
+/* Forward, MXFP8 routed experts (E4M3 + E8M0 scale per 32 along K; shared expert stays BF16).
+ * `*_q` are E4M3 bytes, `*_sc` scale tensors [rows/128, cols/128, 32, 16].  The four "work" tensors
+ * are caller-provided scratch: x_q [MB,H], x_sc, hidden_q [MB,I], hidden_sc.
+ * Reference: mok/ops.py:194-368 (dispatch_mlp_swiglu_combine_fwd_mxfp8),
+ * csrc/mok_megakernel.cuh:1853-1988. */
+typedef struct mok_fwd_mxfp8_args {
+    mok_layer_common c;
+    const uint64_t* x_ptrs;
+    const uint64_t* combine_buffer_ptrs;
+    const void *w_shared_gate, *w_shared_up, *w_shared_down;                 /* bf16 */
+    const void *w_routed_gate_q, *w_routed_gate_sc;                          /* [El,I,H] */
+    const void *w_routed_up_q, *w_routed_up_sc;                              /* [El,I,H] */
+    const void *w_routed_down_q, *w_routed_down_sc;                          /* [El,H,I] */
+    /* outputs */
+    void *x_qt, *x_sct;                                                      /* [H, MB] */
+    void *gate_shared, *up_shared, *hidden_shared;                           /* bf16 [T, I] */
+    void *gate_q, *gate_sc, *up_q, *up_sc;                                   /* [MB, I] */
+    void *hidden_qt, *hidden_sct;                                            /* [I, MB] */
+    void *y_shared, *y_routed;                                               /* bf16 */
+    /* scratch */
+    void *work_x_q, *work_x_sc, *work_hidden_q, *work_hidden_sc;
+} mok_fwd_mxfp8_args;
+int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* args, void* stream);
+
+/* Backward, MXFP8 routed experts.  Weights come pre-transposed for the data gradients
+ * (w_*_T: gate/up as [El,H,I], down as [El,I,H]); the untransposed gate/up weights are only read
+ * when a later macrobatch has to be replayed.
+ * Reference: mok/ops.py:517-808 (dispatch_mlp_swiglu_combine_bwd_mxfp8),
+ * csrc/mok_megakernel.cuh:2546-2777. */
+typedef struct mok_bwd_mxfp8_args {
+    mok_layer_common c;
+    const uint64_t* d_y_ptrs;
+    const uint64_t* d_x_routed_buffer_ptrs;
+    const uint64_t* router_weight_ptrs;
+    const uint64_t* d_router_weight_ptrs;
+    const uint64_t* x_ptrs;
+    const void *w_shared_gate, *w_shared_up, *w_shared_down;
+    const void *w_routed_gate_T_q, *w_routed_gate_T_sc, *w_routed_up_T_q, *w_routed_up_T_sc;
+    const void *w_routed_down_T_q, *w_routed_down_T_sc;
+    const void *w_routed_gate_q, *w_routed_gate_sc, *w_routed_up_q, *w_routed_up_sc;   /* replay */
+    /* saved forward activations (routed ones are overwritten by replay) */
+    void *x_qt, *x_sct, *gate_q, *gate_sc, *up_q, *up_sc, *hidden_qt, *hidden_sct;
+    const void *gate_shared, *up_shared, *hidden_shared;
+    /* outputs */
+    void *d_x_shared, *d_x_routed;
+    void *d_gate_shared, *d_gate_q, *d_gate_sc;
+    void *d_up_shared, *d_up_q, *d_up_sc;
+    void *d_hidden_shared, *d_hidden_routed;
+    void *d_y_q, *d_y_sc;
+    void *d_w_shared_gate, *d_w_shared_up, *d_w_shared_down;
+    void *d_w_routed_gate, *d_w_routed_up, *d_w_routed_down;
+    /* scratch */
+    void *work_x_q, *work_x_sc, *work_hidden_q, *work_hidden_sc;           /* replay */
+    void *work_d_y_qt, *work_d_y_sct, *work_d_gate_qt, *work_d_gate_sct, *work_d_up_qt, *work_d_up_sct;
+    float* router_weights_routed;                                          /* [MB] */
+    float* d_router_weight_partials;                                       /* [MB, I/256] */
+} mok_bwd_mxfp8_args;
+int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* args, void* stream);
+
 /* Launch accounting for benchmarks.  mok_launch_count(): kernels launched by this library since it
  * was loaded.  With mok_profile_enable(1) every launch is bracketed by CUDA events on its stream;
  * mok_profile_collect() waits for them and adds device milliseconds and launch counts per slot
@@ -184,6 +243,11 @@ int mok_profile_collect(double* ms_per_slot, long long* launches_per_slot);
  * M % 128 == 0, N % 256 == 0, K % 64 == 0. */
 int mok_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k,
                   int a_mn_major, int b_mn_major, int32_t* status, void* stream);
+
+/* The same for MXFP8 operands: A [M,K] and B [N,K] as E4M3 bytes with their scale tensors
+ * ([rows/128, K/128, 32, 16]), C bf16.  M % 128 == 0, N % 256 == 0, K % 128 == 0. */
+int mok_gemm_mxfp8(const void* a_fp8, const void* a_sc, const void* b_fp8, const void* b_sc, void* c,
+                   int m, int n, int k, int32_t* status, void* stream);
 
 #ifdef __cplusplus
 }

@@ -3,6 +3,7 @@
 // two HBM-bound epilogues.  All peer traffic is plain unicast ld/st on peer-mapped addresses;
 // there is no cluster multicast and no library collective on this path.
 #include "comm.cuh"
+#include "mxfp8.cuh"
 #include "profile.cuh"
 
 namespace mok {
@@ -187,6 +188,87 @@ __global__ void __launch_bounds__(256) combine_rows_kernel(RowMoveParams p) {
             static_cast<float*>(p.scale_peers.p[pr])[tok] = s;
         }
     }
+}
+
+// dispatch + MXFP8 quantisation.  Work unit = 32 consecutive rows (one MX block along the token axis)
+// x 256 columns, staged in shared memory: coalesced row gathers in, then one normal block and one
+// transposed block per thread out.  Padding rows are zeros (scale byte 88, as the reference's
+// device code produces for an all-zero block).
+template <bool kScale>
+__global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, QuantOut o) {
+    constexpr int kCols = 256, kStride = kCols + 8;
+    __shared__ __align__(16) __nv_bfloat16 tile[32 * kStride];
+    const int n_total = min(*p.num_tokens, p.capacity);
+    const int rows = max(0, min(n_total - p.row_offset, p.row_limit));
+    const int col_chunks = p.hidden / kCols;
+    const int units = (rows / 32) * col_chunks;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+        const int rb = unit / col_chunks, cc = unit - rb * col_chunks;
+        const int row0 = rb * 32, col0 = cc * kCols;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int r = warp * 4 + i;
+            const int g = p.row_offset + row0 + r;
+            const int pr = p.peer_rank[g];
+            uint4 v = make_uint4(0, 0, 0, 0);
+            float w = 0.0f;
+            if (pr >= 0) {
+                const int tok = p.peer_token_idx[g];
+                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.peers.p[pr]) +
+                                                                   static_cast<size_t>(tok / p.row_divisor) * p.hidden + col0);
+                v = src[lane];
+                if (kScale) {
+                    w = static_cast<const float*>(p.scale_peers.p[pr])[tok];
+                    uint32_t* w32 = reinterpret_cast<uint32_t*>(&v);
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float2 f = unpack_bf16(w32[q]);
+                        w32[q] = pack_bf16(f.x * w, f.y * w);
+                    }
+                }
+            }
+            if (kScale && cc == 0 && lane == 0) p.row_scale_out[row0 + r] = w;
+            *reinterpret_cast<uint4*>(&tile[r * kStride + lane * 8]) = v;
+        }
+        __syncthreads();
+        {   // normal: thread -> (row, 32-wide block)
+            const int r = threadIdx.x >> 3, kb = threadIdx.x & 7;
+            uint32_t in[16], out[8], sb;
+            const uint4* src = reinterpret_cast<const uint4*>(&tile[r * kStride + kb * 32]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const uint4 v = src[j]; in[4 * j] = v.x; in[4 * j + 1] = v.y; in[4 * j + 2] = v.z; in[4 * j + 3] = v.w; }
+            mx_quantize_block(in, out, sb);
+            uint4* dst = reinterpret_cast<uint4*>(o.q + static_cast<size_t>(row0 + r) * p.hidden + col0 + kb * 32);
+            dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+            dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+            o.sc[mx_scale_offset(row0 + r, (col0 >> 5) + kb, p.hidden >> 7)] = static_cast<uint8_t>(sb);
+        }
+        {   // transposed: thread -> column, block = the 32 rows
+            const int c = threadIdx.x;
+            uint32_t in[16], out[8], sb;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const uint16_t lo = *reinterpret_cast<const uint16_t*>(&tile[(2 * j) * kStride + c]);
+                const uint16_t hi = *reinterpret_cast<const uint16_t*>(&tile[(2 * j + 1) * kStride + c]);
+                in[j] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+            }
+            mx_quantize_block(in, out, sb);
+            uint4* dst = reinterpret_cast<uint4*>(o.qt + static_cast<size_t>(col0 + c) * o.t_rows + row0);
+            dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+            dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+            o.sct[mx_scale_offset(col0 + c, row0 >> 5, o.t_rows >> 7)] = static_cast<uint8_t>(sb);
+        }
+        __syncthreads();
+    }
+}
+
+int launch_dispatch_quant(const RowMoveParams& p, const QuantOut& out, bool scale, int num_blocks, cudaStream_t stream) {
+    ProfScope prof(kSlotDispatch, stream);
+    if (scale) dispatch_quant_kernel<true><<<num_blocks, 256, 0, stream>>>(p, out);
+    else dispatch_quant_kernel<false><<<num_blocks, 256, 0, stream>>>(p, out);
+    MOK_CUDA_CHECK(cudaGetLastError());
+    return MOK_OK;
 }
 
 int launch_dispatch_rows(const RowMoveParams& p, bool scale, int num_blocks, cudaStream_t stream) {

@@ -27,6 +27,16 @@ struct RowMoveParams {
 };
 
 int launch_dispatch_rows(const RowMoveParams& p, bool scale, int num_blocks, cudaStream_t stream);
+
+// dispatch with fused MXFP8 quantisation: gathered rows are written as E4M3 in both layouts
+// (normal [rows, hidden] with scales along hidden; transposed [hidden, t_rows] with scales along
+// rows) instead of bf16.  `p.local` is unused.
+struct QuantOut {
+    uint8_t* q; uint8_t* sc;      // [row_limit, hidden], [row_limit/128, hidden/128, 512]
+    uint8_t* qt; uint8_t* sct;    // [hidden, t_rows],    [hidden/128, t_rows/128, 512]
+    int t_rows;
+};
+int launch_dispatch_quant(const RowMoveParams& p, const QuantOut& out, bool scale, int num_blocks, cudaStream_t stream);
 int launch_combine_rows(const RowMoveParams& p, int num_blocks, cudaStream_t stream);
 
 }  // namespace mok

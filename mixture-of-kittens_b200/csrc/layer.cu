@@ -11,6 +11,7 @@
 //   ->  dgrad gate+up (one accumulator)  ->  reverse-dispatch (+ router grads)  ->  3 wgrads
 #include "comm.cuh"
 #include "gemm.cuh"
+#include "mxgemm.cuh"
 
 namespace mok {
 namespace {
@@ -293,4 +294,236 @@ extern "C" const char* mok_error_string(int code) {
         case MOK_STATUS_PIPELINE_TIMEOUT: return "kernel pipeline wait timed out";
         default: return "unknown";
     }
+}
+
+// =================================================================================================
+// MXFP8 routed experts.  Same launch sequence as the BF16 passes; the routed GEMMs run block-scaled
+// on E4M3 data, and every producer writes its output already quantised in the layout(s) its
+// consumers contract over: dispatch -> x (normal for gate|up, transposed for the gate/up weight
+// gradients); gate|up epilogue -> saved gate/up, hidden (normal for down, transposed for the down
+// weight gradient); reverse-combine -> w*d_y (normal + transposed); dgrad-down epilogue -> d_gate,
+// d_up (normal + transposed).  The shared expert stays BF16 (as in the reference, ops.py:240-246).
+// =================================================================================================
+namespace mok {
+namespace {
+
+MxGemmParams mx_base(const mok_layer_common& c, int off, int limit) {
+    MxGemmParams p{};
+    p.num_tokens = c.num_tokens;
+    p.capacity = c.schedule_capacity;
+    p.tokens_per_expert = c.tokens_per_expert;
+    p.num_experts = c.num_local_experts;
+    p.row_offset = off;
+    p.row_limit = limit;
+    p.num_segs = 1;
+    p.limit = c.swiglu_limit;
+    p.has_limit = c.has_swiglu_limit;
+    p.status = c.status;
+    p.q_cols = c.intermediate;
+    p.t_rows = c.macrobatch_size;
+    return p;
+}
+inline uint8_t* u8(void* p) { return static_cast<uint8_t*>(p); }
+inline const uint8_t* cu8(const void* p) { return static_cast<const uint8_t*>(p); }
+
+int mx_gate_up(const mok_layer_common& c, const Dims& d, int off, int limit, const void* x_q, const void* x_sc,
+               const void* wg_q, const void* wg_sc, const void* wu_q, const void* wu_sc, void* gate_q, void* gate_sc,
+               void* up_q, void* up_sc, void* hid_q, void* hid_sc, void* hid_qt, void* hid_sct, cudaStream_t s) {
+    MxGemmParams p = mx_base(c, off, limit);
+    p.n_tiles = d.I / (kBlockN / 2);
+    p.k_tiles_per_seg = d.H / kMxBlockK;
+    p.b_rows_per_expert = d.I;
+    p.sfa0 = cu8(x_sc); p.sfa_k_tiles = d.H / 128;
+    p.sfb0 = cu8(wg_sc); p.sfb1 = cu8(wu_sc); p.sfb_k_tiles = d.H / 128;
+    p.q[0] = u8(gate_q); p.sc[0] = u8(gate_sc);
+    p.q[1] = u8(up_q); p.sc[1] = u8(up_sc);
+    p.q[2] = u8(hid_q); p.sc[2] = u8(hid_sc);
+    p.qt[2] = u8(hid_qt); p.sct[2] = u8(hid_sct);
+    MxGemmOperands o{};
+    o.a0 = x_q; o.b0 = wg_q; o.b1 = wu_q;
+    o.a_inner = d.H; o.a_outer = d.MB;
+    o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(d.El) * d.I;
+    return launch_mx_gemm(kMxEpiGateUp, false, o, p, (limit / kBlockM) * p.n_tiles, 0, kSlotGateUpRouted, s);
+}
+
+int mx_down(const mok_layer_common& c, const Dims& d, int off, int limit, const void* hid_q, const void* hid_sc,
+            const void* wd_q, const void* wd_sc, void* y, cudaStream_t s) {
+    MxGemmParams p = mx_base(c, off, limit);
+    p.n_tiles = d.H / kBlockN;
+    p.k_tiles_per_seg = d.I / kMxBlockK;
+    p.b_rows_per_expert = d.H;
+    p.sfa0 = cu8(hid_sc); p.sfa_k_tiles = d.I / 128;
+    p.sfb0 = cu8(wd_sc); p.sfb_k_tiles = d.I / 128;
+    p.out_bf16 = static_cast<__nv_bfloat16*>(y);
+    p.ld_out = d.H;
+    MxGemmOperands o{};
+    o.a0 = hid_q; o.b0 = wd_q;
+    o.a_inner = d.I; o.a_outer = d.MB;
+    o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(d.El) * d.H;
+    return launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0, kSlotDownRouted, s);
+}
+
+int mx_wgrad(const mok_layer_common& c, const Dims& d, int off, int limit, const void* a_qt, const void* a_sct, int m,
+             const void* b_qt, const void* b_sct, int n, void* dw, int accumulate, cudaStream_t s) {
+    MxGemmParams p = mx_base(c, off, limit);
+    p.m_tiles_w = m / kBlockM;
+    p.n_tiles = n / kBlockN;
+    p.sfa0 = cu8(a_sct); p.sfa_k_tiles = d.MB / 128;
+    p.sfb0 = cu8(b_sct); p.sfb_k_tiles = d.MB / 128;
+    p.out_bf16 = static_cast<__nv_bfloat16*>(dw);
+    p.ld_out = n;
+    p.out_expert_stride = static_cast<long long>(m) * n;
+    p.accumulate = accumulate;
+    MxGemmOperands o{};
+    o.a0 = a_qt; o.b0 = b_qt;
+    o.a_inner = d.MB; o.a_outer = m;
+    o.b_inner = d.MB; o.b_outer = n;
+    return launch_mx_gemm(kMxEpiStore, true, o, p, d.El * p.m_tiles_w * p.n_tiles, 0, kSlotWgradRouted, s);
+}
+
+}  // namespace
+}  // namespace mok
+
+extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
+    if (!a) return MOK_ERR_INVALID;
+    Dims d;
+    MOK_TRY(check_common(a->c, d));
+    if (d.MB % 128 || d.H % 128 || d.I % 128) return MOK_ERR_INVALID;
+    const mok_layer_common& c = a->c;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    PeerPtrs x_peers{}, combine_peers{};
+    MOK_TRY(fill_peers(x_peers, a->x_ptrs, d.W));
+    MOK_TRY(fill_peers(combine_peers, a->combine_buffer_ptrs, d.W));
+    const void* x_local = x_peers.p[d.rank];
+    const int move_blocks = device_sm_count() * 4;
+
+    MOK_TRY(run_gate_up(c, d, false, 0, d.T, x_local, d.T, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
+                        a->hidden_shared, s));
+    MOK_TRY(run_down(c, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
+
+    const int n_macro = (d.cap + d.MB - 1) / d.MB;
+    for (int m = n_macro - 1; m >= 0; --m) {
+        const int off = m * d.MB;
+        const int limit = std::min(d.MB, d.cap - off);
+        RowMoveParams disp = row_move(c, d, off, limit, nullptr);
+        disp.peers = x_peers;
+        disp.row_divisor = d.K;
+        QuantOut xo{u8(a->work_x_q), u8(a->work_x_sc), u8(a->x_qt), u8(a->x_sct), d.MB};
+        MOK_TRY(launch_dispatch_quant(disp, xo, false, move_blocks, s));
+        MOK_TRY(mx_gate_up(c, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
+                           a->w_routed_up_q, a->w_routed_up_sc, a->gate_q, a->gate_sc, a->up_q, a->up_sc, a->work_hidden_q,
+                           a->work_hidden_sc, a->hidden_qt, a->hidden_sct, s));
+        MOK_TRY(mx_down(c, d, off, limit, a->work_hidden_q, a->work_hidden_sc, a->w_routed_down_q, a->w_routed_down_sc,
+                        a->y_routed, s));
+        RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
+        comb.peers = combine_peers;
+        MOK_TRY(launch_combine_rows(comb, move_blocks, s));
+    }
+    return MOK_OK;
+}
+
+extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
+    if (!a) return MOK_ERR_INVALID;
+    Dims d;
+    MOK_TRY(check_common(a->c, d));
+    if (d.MB % 128 || d.H % 128 || d.I % 128) return MOK_ERR_INVALID;
+    const mok_layer_common& c = a->c;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    PeerPtrs dy_peers{}, dxr_peers{}, rw_peers{}, drw_peers{}, x_peers{};
+    MOK_TRY(fill_peers(dy_peers, a->d_y_ptrs, d.W));
+    MOK_TRY(fill_peers(dxr_peers, a->d_x_routed_buffer_ptrs, d.W));
+    MOK_TRY(fill_peers(rw_peers, a->router_weight_ptrs, d.W));
+    MOK_TRY(fill_peers(drw_peers, a->d_router_weight_ptrs, d.W));
+    MOK_TRY(fill_peers(x_peers, a->x_ptrs, d.W));
+    if (!a->router_weights_routed || !a->d_router_weight_partials) return MOK_ERR_INVALID;
+    const void* dy_local = dy_peers.p[d.rank];
+    const void* x_local = x_peers.p[d.rank];
+    const int move_blocks = device_sm_count() * 4;
+    const int partial_cols = d.I / kBlockN;
+
+    // shared expert, BF16
+    MOK_TRY(run_dgrad_down(c, d, false, 0, d.T, dy_local, d.T, a->w_shared_down, a->gate_shared, a->up_shared,
+                           a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, nullptr, s));
+    MOK_TRY(run_dgrad_gate_up(c, d, false, 0, d.T, a->d_gate_shared, a->d_up_shared, d.T, a->w_shared_gate, a->w_shared_up,
+                              a->d_x_shared, s));
+    MOK_TRY(run_wgrad(c, false, 0, d.T, dy_local, d.H, a->hidden_shared, d.I, d.T, a->d_w_shared_down, 0, s));
+    MOK_TRY(run_wgrad(c, false, 0, d.T, a->d_gate_shared, d.I, x_local, d.H, d.T, a->d_w_shared_gate, 0, s));
+    MOK_TRY(run_wgrad(c, false, 0, d.T, a->d_up_shared, d.I, x_local, d.H, d.T, a->d_w_shared_up, 0, s));
+
+    const int n_macro = (d.cap + d.MB - 1) / d.MB;
+    for (int m = 0; m < n_macro; ++m) {
+        const int off = m * d.MB;
+        const int limit = std::min(d.MB, d.cap - off);
+        if (m > 0) {   // replay dispatch + gate|up of this window into the saved-activation buffers
+            RowMoveParams disp = row_move(c, d, off, limit, nullptr);
+            disp.peers = x_peers;
+            disp.row_divisor = d.K;
+            QuantOut xo{u8(a->work_x_q), u8(a->work_x_sc), u8(a->x_qt), u8(a->x_sct), d.MB};
+            MOK_TRY(launch_dispatch_quant(disp, xo, false, move_blocks, s));
+            MOK_TRY(mx_gate_up(c, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
+                               a->w_routed_up_q, a->w_routed_up_sc, a->gate_q, a->gate_sc, a->up_q, a->up_sc,
+                               a->work_hidden_q, a->work_hidden_sc, a->hidden_qt, a->hidden_sct, s));
+        }
+        // reverse-combine: w * d_y, quantised in both layouts
+        RowMoveParams rc = row_move(c, d, off, limit, nullptr);
+        rc.peers = dy_peers;
+        rc.scale_peers = rw_peers;
+        rc.row_divisor = d.K;
+        rc.row_scale_out = a->router_weights_routed;
+        QuantOut dyo{u8(a->d_y_q), u8(a->d_y_sc), u8(a->work_d_y_qt), u8(a->work_d_y_sct), d.MB};
+        MOK_TRY(launch_dispatch_quant(rc, dyo, true, move_blocks, s));
+        {   // d_hidden = d_y @ Wd^T' (pre-transposed [El, I, H]) + SwiGLU backward
+            MxGemmParams p = mx_base(c, off, limit);
+            p.n_tiles = d.I / kBlockN;
+            p.k_tiles_per_seg = d.H / kMxBlockK;
+            p.b_rows_per_expert = d.I;
+            p.sfa0 = cu8(a->d_y_sc); p.sfa_k_tiles = d.H / 128;
+            p.sfb0 = cu8(a->w_routed_down_T_sc); p.sfb_k_tiles = d.H / 128;
+            p.out_bf16 = static_cast<__nv_bfloat16*>(a->d_hidden_routed);
+            p.ld_out = d.I;
+            p.in_q[0] = cu8(a->gate_q); p.in_sc[0] = cu8(a->gate_sc);
+            p.in_q[1] = cu8(a->up_q); p.in_sc[1] = cu8(a->up_sc);
+            p.q[0] = u8(a->d_gate_q); p.sc[0] = u8(a->d_gate_sc);
+            p.q[1] = u8(a->d_up_q); p.sc[1] = u8(a->d_up_sc);
+            p.qt[0] = u8(a->work_d_gate_qt); p.sct[0] = u8(a->work_d_gate_sct);
+            p.qt[1] = u8(a->work_d_up_qt); p.sct[1] = u8(a->work_d_up_sct);
+            p.row_scale = a->router_weights_routed;
+            p.partials = a->d_router_weight_partials;
+            MxGemmOperands o{};
+            o.a0 = a->d_y_q; o.b0 = a->w_routed_down_T_q;
+            o.a_inner = d.H; o.a_outer = d.MB;
+            o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(d.El) * d.I;
+            MOK_TRY(launch_mx_gemm(kMxEpiDgradDown, false, o, p, (limit / kBlockM) * p.n_tiles, 0, kSlotDgradDownRouted, s));
+        }
+        {   // d_x = d_gate @ Wg^T' + d_up @ Wu^T' (pre-transposed [El, H, I]) in one accumulator
+            MxGemmParams p = mx_base(c, off, limit);
+            p.n_tiles = d.H / kBlockN;
+            p.k_tiles_per_seg = d.I / kMxBlockK;
+            p.num_segs = 2;
+            p.b_rows_per_expert = d.H;
+            p.sfa0 = cu8(a->d_gate_sc); p.sfa1 = cu8(a->d_up_sc); p.sfa_k_tiles = d.I / 128;
+            p.sfb0 = cu8(a->w_routed_gate_T_sc); p.sfb1 = cu8(a->w_routed_up_T_sc); p.sfb_k_tiles = d.I / 128;
+            p.out_bf16 = static_cast<__nv_bfloat16*>(a->d_x_routed);
+            p.ld_out = d.H;
+            MxGemmOperands o{};
+            o.a0 = a->d_gate_q; o.a1 = a->d_up_q; o.b0 = a->w_routed_gate_T_q; o.b1 = a->w_routed_up_T_q;
+            o.a_inner = d.I; o.a_outer = d.MB;
+            o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(d.El) * d.H;
+            MOK_TRY(launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0, kSlotDgradGateUpRouted, s));
+        }
+        RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
+        rd.peers = dxr_peers;
+        rd.scale_peers = drw_peers;
+        rd.partials = a->d_router_weight_partials;
+        rd.partial_cols = partial_cols;
+        MOK_TRY(launch_combine_rows(rd, move_blocks, s));
+        const int acc = m > 0 ? 1 : 0;
+        MOK_TRY(mx_wgrad(c, d, off, limit, a->work_d_y_qt, a->work_d_y_sct, d.H, a->hidden_qt, a->hidden_sct, d.I,
+                         a->d_w_routed_down, acc, s));
+        MOK_TRY(mx_wgrad(c, d, off, limit, a->work_d_gate_qt, a->work_d_gate_sct, d.I, a->x_qt, a->x_sct, d.H,
+                         a->d_w_routed_gate, acc, s));
+        MOK_TRY(mx_wgrad(c, d, off, limit, a->work_d_up_qt, a->work_d_up_sct, d.I, a->x_qt, a->x_sct, d.H,
+                         a->d_w_routed_up, acc, s));
+    }
+    return MOK_OK;
 }

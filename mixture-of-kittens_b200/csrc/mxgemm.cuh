@@ -1,0 +1,400 @@
+// Persistent grouped GEMM for MXFP8 operands on tcgen05: E4M3 data, one E8M0 scale per 32
+// elements along K (tcgen05.mma kind::mxf8f6f4.block_scale), fp32 accumulation in tensor memory.
+//
+// Both operands are always K-major (the layer keeps transposed-quantised copies where the
+// contraction runs over tokens), so one shared-memory layout serves every GEMM of the layer:
+//   A tile 128 rows x 128 B, B tile 256 rows x 128 B, 128-byte swizzle, loaded by TMA;
+//   scale tiles (512 B per 128 rows x 128 K, already in the tcgen05 [32][16] layout in global
+//   memory) are fetched with cp.async.bulk and copied shared -> tensor memory by tcgen05.cp
+//   (32x128b, replicated over the four lane quarters) right before the four K=32 MMAs of a stage.
+// Tensor memory: accumulator columns [0,256), A scales [256,260), B scales [260,268).  There is
+// no room for a second 256-column accumulator beside the scales, so the epilogue warps first pull
+// the whole accumulator into registers as packed bf16 (the layer rounds GEMM outputs to bf16
+// before any further use anyway), release it, and only then run the fused epilogue — the next
+// tile's main loop overlaps everything but that read-out.
+//
+// Fused epilogues:
+//   Store      bf16 C (optionally accumulating onto the stored bf16 value: weight gradients)
+//   GateUp     tile = (gate | up) halves -> saved gate/up as MXFP8, hidden = SwiGLU as MXFP8 in
+//              both layouts (normal for the down GEMM, transposed for the down weight gradient)
+//   DgradDown  d_hidden bf16 + SwiGLU backward from the saved MXFP8 gate/up -> d_gate, d_up as
+//              MXFP8 in both layouts + router-gradient partial sums
+// A warp's 32 lanes own 32 consecutive rows, i.e. exactly one MX block along the token axis, so
+// the transposed quantisation needs only a warp-wide max (redux.sync) per column.
+#pragma once
+
+#include "gemm.cuh"
+#include "mxfp8.cuh"
+
+namespace mok {
+
+enum : int { kMxEpiStore = 0, kMxEpiGateUp = 1, kMxEpiDgradDown = 2 };
+
+constexpr int kMxBlockK = 128;                        // bytes (= elements) of K per stage
+constexpr int kMxABytes = kBlockM * kMxBlockK;        // 16 KB
+constexpr int kMxBBytes = kBlockN * kMxBlockK;        // 32 KB
+constexpr int kMxTileBytes = kMxABytes + kMxBBytes;
+constexpr int kMxSfBytes = 512 + 1024;                // A scales + B scales per stage
+constexpr int kMxSmemBytes = kStages * (kMxTileBytes + kMxSfBytes) + 256 + kMaxExperts * 4 + 1024;
+constexpr int kMxAccCols = 256, kMxSfaCol = 256, kMxSfbCol = 260;
+
+struct MxGemmParams {
+    // row domain (same meaning as GemmParams)
+    const int* num_tokens;
+    int rows_host, capacity, row_offset, row_limit;
+    const int* tokens_per_expert;
+    int num_experts;
+    // tiling
+    int n_tiles, m_tiles_w, k_tiles_per_seg, num_segs, b_rows_per_expert;
+    // scales: [row_tiles, k_tiles, 512 B]
+    const uint8_t* sfa0; const uint8_t* sfa1; int sfa_k_tiles;
+    const uint8_t* sfb0; const uint8_t* sfb1; int sfb_k_tiles;
+    // Store / DgradDown: bf16 output
+    __nv_bfloat16* out_bf16;
+    int ld_out;
+    long long out_expert_stride;
+    int accumulate;
+    // quantised outputs: index 0 = gate or d_gate, 1 = up or d_up, 2 = hidden
+    uint8_t* q[3]; uint8_t* sc[3];          // normal layout [rows, cols], scales [rows/128, cols/128, 512]
+    uint8_t* qt[3]; uint8_t* sct[3];        // transposed layout [cols, t_rows], scales [cols/128, t_rows/128, 512]
+    int q_cols;                             // intermediate size I
+    int t_rows;                             // macrobatch size (row length of the transposed tensors)
+    // DgradDown inputs: saved gate / up
+    const uint8_t* in_q[2]; const uint8_t* in_sc[2];
+    const float* row_scale;
+    float* partials;
+    float limit;
+    int has_limit;
+    int* status;
+};
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+// descriptor of a dense 32 x 16-byte scale block for tcgen05.cp (no swizzle, 8-row groups 128 B apart)
+__device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3FFFF) >> 4);
+    d |= static_cast<uint64_t>(128 >> 4) << 32;
+    d |= 1ull << 46;
+    return d;
+}
+
+// quantise one 32-wide chunk of a row (16 packed bf16 words) along the row and store bytes + scale
+__device__ __forceinline__ void mx_store_normal(const uint32_t (&w)[16], uint8_t* q, uint8_t* sc, size_t row, int col0, int cols) {
+    uint32_t out[8], sb;
+    mx_quantize_block(w, out, sb);
+    uint4* dst = reinterpret_cast<uint4*>(q + row * cols + col0);
+    dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+    dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+    sc[mx_scale_offset(static_cast<int>(row), col0 >> 5, cols >> 7)] = static_cast<uint8_t>(sb);
+}
+// quantise the same chunk along the token axis: the warp's 32 lanes hold rows row0..row0+31 (one MX
+// block) of 32 columns; column j's block is reduced with redux.sync and written to qt[col0+j][row]
+__device__ __forceinline__ void mx_store_transposed(const uint32_t (&w)[16], uint8_t* qt, uint8_t* sct, size_t row, int col0,
+                                                    int t_rows, int lane) {
+    uint32_t my_scale = 0;
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+        const uint32_t word = w[j >> 1];
+        const uint32_t bits = ((j & 1) ? (word & 0xFFFF0000u) : (word << 16));      // bf16 -> fp32 bit pattern
+        const uint32_t amax_bits = __reduce_max_sync(0xffffffffu, bits & 0x7FFFFFFFu);
+        const uint32_t sb = mx_scale_byte(__uint_as_float(amax_bits));
+        const float v = __uint_as_float(bits) * mx_inv_scale(sb);
+        qt[static_cast<size_t>(col0 + j) * t_rows + row] = static_cast<uint8_t>(mx_pack2(v, 0.0f) & 0xFFu);
+        if (lane == j) my_scale = sb;
+    }
+    sct[mx_scale_offset(col0 + lane, static_cast<int>(row >> 5), t_rows >> 7)] = static_cast<uint8_t>(my_scale);
+}
+
+template <int kEpi, bool kWgrad>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
+               const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
+               const MxGemmParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+    uint8_t* sf_smem = smem + kStages * kMxTileBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(sf_smem + kStages * kMxSfBytes);
+    uint64_t* empty_bar = full_bar + kStages;
+    uint64_t* tfull_bar = empty_bar + kStages;
+    uint64_t* tempty_bar = tfull_bar + 1;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    int* s_end = reinterpret_cast<int*>(sf_smem + kStages * kMxSfBytes + 256);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int E = p.tokens_per_expert ? p.num_experts : 1;
+    if (p.tokens_per_expert) {
+        for (int e = threadIdx.x; e < E; e += blockDim.x) s_end[e] = p.tokens_per_expert[e];
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        mbar_init(tfull_bar, 1);
+        mbar_init(tempty_bar, 4);
+        *abort_flag = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (warp == 0 && p.tokens_per_expert) {
+        const int per = (E + 31) / 32;
+        int sum = 0;
+        for (int j = 0; j < per; ++j) { const int e = lane * per + j; if (e < E) sum += s_end[e]; }
+        int incl = sum;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) { const int n = __shfl_up_sync(0xffffffffu, incl, off); if (lane >= off) incl += n; }
+        int run = incl - sum;
+        for (int j = 0; j < per; ++j) { const int e = lane * per + j; if (e < E) { run += s_end[e]; s_end[e] = run; } }
+    }
+    if (warp == 1) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int n_total = p.num_tokens ? min(*p.num_tokens, p.capacity) : p.rows_host;
+    const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
+    const int num_tiles = kWgrad ? ((p.accumulate && win_rows == 0) ? 0 : E * p.m_tiles_w * p.n_tiles)
+                                 : (win_rows / kBlockM) * p.n_tiles;
+
+    auto decode = [&](int tile, int& m_idx, int& n_idx, int& expert, int& k_row0, int& k_tiles) {
+        if constexpr (kWgrad) {
+            const int per_e = p.m_tiles_w * p.n_tiles;
+            expert = tile / per_e;
+            const int r = tile - expert * per_e;
+            m_idx = r / p.n_tiles;
+            n_idx = r - m_idx * p.n_tiles;
+            int s = 0, e_end = n_total;
+            if (p.tokens_per_expert) { s = expert ? s_end[expert - 1] : 0; e_end = min(s_end[expert], n_total); }
+            const int lo = max(s, p.row_offset), hi = min(e_end, p.row_offset + win_rows);
+            k_row0 = lo - p.row_offset;
+            k_tiles = hi > lo ? (hi - lo) / kMxBlockK : 0;
+        } else {
+            m_idx = tile / p.n_tiles;
+            n_idx = tile - m_idx * p.n_tiles;
+            expert = 0;
+            if (p.tokens_per_expert) {
+                const int g = p.row_offset + m_idx * kBlockM;
+                int lo = 0, hi = E - 1;
+                while (lo < hi) { const int mid = (lo + hi) >> 1; if (s_end[mid] > g) hi = mid; else lo = mid + 1; }
+                expert = lo;
+            }
+            k_row0 = 0;
+            k_tiles = p.k_tiles_per_seg * p.num_segs;
+        }
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            tma_prefetch_desc(&tmA0); tma_prefetch_desc(&tmB0);
+            int stage = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int m_idx, n_idx, expert, k_row0, k_tiles;
+                decode(tile, m_idx, n_idx, expert, k_row0, k_tiles);
+                for (int kt = 0; kt < k_tiles; ++kt) {
+                    if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* sa = smem + stage * kMxTileBytes;
+                    uint8_t* sb = sa + kMxABytes;
+                    uint8_t* ssfa = sf_smem + stage * kMxSfBytes;
+                    uint8_t* ssfb = ssfa + 512;
+                    mbar_arrive_expect_tx(&full_bar[stage], kMxTileBytes + kMxSfBytes);
+                    const int seg = (!kWgrad && kt >= p.k_tiles_per_seg) ? 1 : 0;
+                    const int kt_seg = kWgrad ? kt : kt - seg * p.k_tiles_per_seg;
+                    const int k_tile_abs = (kWgrad ? k_row0 / kMxBlockK : 0) + kt_seg;      // k-tile index in the tensors
+                    const CUtensorMap* ma = seg ? &tmA1 : &tmA0;
+                    const CUtensorMap* mb = seg ? &tmB1 : &tmB0;
+                    const uint8_t* sfa = seg ? p.sfa1 : p.sfa0;
+                    const uint8_t* sfb = seg ? p.sfb1 : p.sfb0;
+                    tma_load_2d(sa, ma, &full_bar[stage], k_tile_abs * kMxBlockK, m_idx * kBlockM);
+                    bulk_load_1d(ssfa, sfa + (static_cast<size_t>(m_idx) * p.sfa_k_tiles + k_tile_abs) * 512, 512, &full_bar[stage]);
+                    if constexpr (kEpi == kMxEpiGateUp) {
+                        const int y = expert * p.b_rows_per_expert + n_idx * (kBlockN / 2);
+                        tma_load_2d(sb, &tmB0, &full_bar[stage], k_tile_abs * kMxBlockK, y);
+                        tma_load_2d(sb + kMxBBytes / 2, &tmB1, &full_bar[stage], k_tile_abs * kMxBlockK, y);
+                        const size_t so = (static_cast<size_t>(y >> 7) * p.sfb_k_tiles + k_tile_abs) * 512;
+                        bulk_load_1d(ssfb, p.sfb0 + so, 512, &full_bar[stage]);
+                        bulk_load_1d(ssfb + 512, p.sfb1 + so, 512, &full_bar[stage]);
+                    } else {
+                        const int y = (kWgrad ? 0 : expert * p.b_rows_per_expert) + n_idx * kBlockN;
+                        tma_load_2d(sb, mb, &full_bar[stage], k_tile_abs * kMxBlockK, y);
+                        const size_t so = (static_cast<size_t>(y >> 7) * p.sfb_k_tiles + k_tile_abs) * 512;
+                        bulk_load_1d(ssfb, sfb + so, 512, &full_bar[stage]);
+                        bulk_load_1d(ssfb + 512, sfb + so + static_cast<size_t>(p.sfb_k_tiles) * 512, 512, &full_bar[stage]);
+                    }
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_mxf8(kBlockM, kBlockN, 0, 0);
+            int stage = 0; uint32_t phase = 0;
+            int it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+                int m_idx, n_idx, expert, k_row0, k_tiles;
+                decode(tile, m_idx, n_idx, expert, k_row0, k_tiles);
+                if (!mbar_wait(tempty_bar, (it & 1) ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after();
+                for (int kt = 0; kt < k_tiles; ++kt) {
+                    if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint32_t sa = smem_u32(smem + stage * kMxTileBytes);
+                    const uint32_t sb = sa + kMxABytes;
+                    const uint32_t ssf = smem_u32(sf_smem + stage * kMxSfBytes);
+                    tmem_cp_32x128b_warpx4(tmem_base + kMxSfaCol, make_sf_desc(ssf));
+                    tmem_cp_32x128b_warpx4(tmem_base + kMxSfbCol, make_sf_desc(ssf + 512));
+                    tmem_cp_32x128b_warpx4(tmem_base + kMxSfbCol + 4, make_sf_desc(ssf + 1024));
+                    const uint64_t adesc = make_smem_desc(sa, 16, 1024);
+                    const uint64_t bdesc = make_smem_desc(sb, 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < kMxBlockK / 32; ++k) {
+                        const uint32_t id = idesc | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
+                        umma_mxf8(tmem_base, adesc + ((k * 32) >> 4), bdesc + ((k * 32) >> 4), id, tmem_base + kMxSfaCol,
+                                  tmem_base + kMxSfbCol, (kt > 0 || k > 0) ? 1u : 0u);
+                    }
+                    umma_commit(&empty_bar[stage]);
+                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                if (k_tiles > 0) umma_commit(tfull_bar);
+                else mbar_arrive(tfull_bar);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps
+        const int quarter = warp & 3;
+        const int r_in_tile = quarter * 32 + lane;
+        int it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            int m_idx, n_idx, expert, k_row0, k_tiles;
+            decode(tile, m_idx, n_idx, expert, k_row0, k_tiles);
+            if (!mbar_wait(tfull_bar, it & 1, abort_flag)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
+            uint32_t pk[128];     // the thread's accumulator row as packed bf16 pairs
+#pragma unroll
+            for (int c = 0; c < kBlockN / 32; ++c) {
+                uint32_t acc[32];
+                if (k_tiles > 0) { tmem_ld_32x32(t_addr + c * 32, acc); tmem_ld_wait(); }
+                else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) acc[i] = 0u;
+                }
+#pragma unroll
+                for (int i = 0; i < 16; ++i) pk[c * 16 + i] = pack_bf16(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(tempty_bar);      // accumulator is free for the next tile
+
+            const size_t row = static_cast<size_t>(m_idx) * kBlockM + r_in_tile;
+            if constexpr (kEpi == kMxEpiStore) {
+                if (!(kWgrad && p.accumulate && k_tiles == 0)) {
+                    __nv_bfloat16* dst = p.out_bf16 + (kWgrad ? static_cast<size_t>(expert) * p.out_expert_stride : 0) +
+                                         row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN;
+                    uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+                    for (int v = 0; v < 32; ++v) {
+                        uint32_t o[4] = {pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]};
+                        if (kWgrad && p.accumulate) {
+                            const uint4 old = d4[v];
+                            const uint32_t q[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                const float2 a = unpack_bf16(o[i]), b = unpack_bf16(q[i]);
+                                o[i] = pack_bf16(a.x + b.x, a.y + b.y);
+                            }
+                        }
+                        d4[v] = make_uint4(o[0], o[1], o[2], o[3]);
+                    }
+                }
+            } else if constexpr (kEpi == kMxEpiGateUp) {
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const int col0 = n_idx * (kBlockN / 2) + c * 32;
+                    uint32_t g[16], u[16], h[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        g[i] = pk[c * 16 + i];
+                        u[i] = pk[64 + c * 16 + i];
+                        float2 gf = unpack_bf16(g[i]), uf = unpack_bf16(u[i]);
+                        if (p.has_limit) {
+                            gf.x = fminf(gf.x, p.limit); gf.y = fminf(gf.y, p.limit);
+                            uf.x = fminf(fmaxf(uf.x, -p.limit), p.limit); uf.y = fminf(fmaxf(uf.y, -p.limit), p.limit);
+                        }
+                        h[i] = pack_bf16(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
+                    }
+                    mx_store_normal(g, p.q[0], p.sc[0], row, col0, p.q_cols);
+                    mx_store_normal(u, p.q[1], p.sc[1], row, col0, p.q_cols);
+                    mx_store_normal(h, p.q[2], p.sc[2], row, col0, p.q_cols);
+                    mx_store_transposed(h, p.qt[2], p.sct[2], row, col0, p.t_rows, lane);
+                }
+            } else {
+                float inv_w = 0.0f;
+                if (p.row_scale) { const float w = p.row_scale[row]; inv_w = w > 0.0f ? 1.0f / w : 0.0f; }
+                float partial = 0.0f;
+                uint4* dh4 = reinterpret_cast<uint4*>(p.out_bf16 + row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN);
+#pragma unroll
+                for (int c = 0; c < 8; ++c) {
+                    const int col0 = n_idx * kBlockN + c * 32;
+                    const uint4* gq = reinterpret_cast<const uint4*>(p.in_q[0] + row * p.q_cols + col0);
+                    const uint4* uq = reinterpret_cast<const uint4*>(p.in_q[1] + row * p.q_cols + col0);
+                    const uint4 g0 = gq[0], g1 = gq[1], u0 = uq[0], u1 = uq[1];
+                    const size_t so = mx_scale_offset(static_cast<int>(row), col0 >> 5, p.q_cols >> 7);
+                    const float gs = mx_scale_value(p.in_sc[0][so]), us = mx_scale_value(p.in_sc[1][so]);
+                    const uint32_t gb[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+                    const uint32_t ub[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+                    uint32_t dg[16], du[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint16_t g2 = static_cast<uint16_t>(gb[i >> 1] >> ((i & 1) * 16));
+                        const uint16_t u2 = static_cast<uint16_t>(ub[i >> 1] >> ((i & 1) * 16));
+                        float2 gf = mx_unpack2(g2, gs), uf = mx_unpack2(u2, us);
+                        const float2 dhf = unpack_bf16(pk[c * 16 + i]);
+                        bool gm0 = true, gm1 = true, um0 = true, um1 = true;
+                        if (p.has_limit) {
+                            gm0 = gf.x <= p.limit; gm1 = gf.y <= p.limit;
+                            um0 = uf.x >= -p.limit && uf.x <= p.limit; um1 = uf.y >= -p.limit && uf.y <= p.limit;
+                            gf.x = fminf(gf.x, p.limit); gf.y = fminf(gf.y, p.limit);
+                            uf.x = fminf(fmaxf(uf.x, -p.limit), p.limit); uf.y = fminf(fmaxf(uf.y, -p.limit), p.limit);
+                        }
+                        const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x)), s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+                        const float silu0 = gf.x * s0, silu1 = gf.y * s1;
+                        const float ds0 = (1.0f - silu0) * s0 + silu0, ds1 = (1.0f - silu1) * s1 + silu1;
+                        dg[i] = pack_bf16(gm0 ? ds0 * uf.x * dhf.x : 0.0f, gm1 ? ds1 * uf.y * dhf.y : 0.0f);
+                        du[i] = pack_bf16(um0 ? silu0 * dhf.x : 0.0f, um1 ? silu1 * dhf.y : 0.0f);
+                        partial += dhf.x * inv_w * (silu0 * uf.x) + dhf.y * inv_w * (silu1 * uf.y);
+                    }
+#pragma unroll
+                    for (int v = 0; v < 4; ++v)
+                        dh4[c * 4 + v] = make_uint4(pk[c * 16 + 4 * v], pk[c * 16 + 4 * v + 1], pk[c * 16 + 4 * v + 2], pk[c * 16 + 4 * v + 3]);
+                    mx_store_normal(dg, p.q[0], p.sc[0], row, col0, p.q_cols);
+                    mx_store_normal(du, p.q[1], p.sc[1], row, col0, p.q_cols);
+                    mx_store_transposed(dg, p.qt[0], p.sct[0], row, col0, p.t_rows, lane);
+                    mx_store_transposed(du, p.qt[1], p.sct[1], row, col0, p.t_rows, lane);
+                }
+                if (p.partials) p.partials[row * p.n_tiles + n_idx] = partial;
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+    if (threadIdx.x == 0 && *abort_flag) report_status(p.status, MOK_STATUS_PIPELINE_TIMEOUT, 100 + warp);
+}
+
+struct MxGemmOperands {
+    const void* a0; const void* b0; const void* a1; const void* b1;
+    uint64_t a_inner, a_outer, b_inner, b_outer;      // bytes of K per row, rows
+};
+int launch_mx_gemm(int epi, bool wgrad, const MxGemmOperands& ops, const MxGemmParams& p, int max_tiles, int max_ctas,
+                   int prof_slot, cudaStream_t stream);
+
+}  // namespace mok

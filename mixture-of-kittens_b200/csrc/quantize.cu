@@ -4,34 +4,10 @@
 //   scale = max(amax * 0.002232142857f, 1e-12f); e = cvt.rp.satfinite.ue8m0(scale);
 //   q = cvt.rn.satfinite.e4m3(x * 2^(127-e)).
 // HBM-bound: reads 2 B/element once, writes 1 B/element per requested layout (+1/32 for scales).
-#include "common.cuh"
+#include "mxfp8.cuh"
 #include "profile.cuh"
 
 namespace mok {
-
-// 32 bf16 values (16 packed words) -> 32 fp8 bytes (8 words) + the E8M0 scale byte
-__device__ __forceinline__ void mx_quantize_block(const uint32_t (&in)[16], uint32_t (&out)[8], uint32_t& scale_byte) {
-    float amax = 0.0f;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const float2 v = unpack_bf16(in[i]);
-        amax = fmaxf(amax, fmaxf(fabsf(v.x), fabsf(v.y)));
-    }
-    const float scale = fmaxf(amax * 0.002232142857f, 0.000000000001f);
-    uint16_t sc2;
-    asm volatile("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(sc2) : "f"(scale), "f"(scale));
-    scale_byte = sc2 & 0xFFu;
-    const float inv = __uint_as_float((254u - scale_byte) << 23);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const float2 a = unpack_bf16(in[2 * i]);
-        const float2 b = unpack_bf16(in[2 * i + 1]);
-        uint16_t lo, hi;
-        asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(lo) : "f"(a.x * inv), "f"(a.y * inv));
-        asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(hi) : "f"(b.x * inv), "f"(b.y * inv));
-        out[i] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
-    }
-}
 
 namespace {
 

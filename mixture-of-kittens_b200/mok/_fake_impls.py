@@ -80,3 +80,33 @@ def _(y_shared, combine_buffer, topk_weights):
 @_fake("mok::bwd_epilogue")
 def _(d_x_shared, d_x_routed_buffer):
     return torch.empty_like(d_x_shared)
+
+
+@_fake("mok::dispatch_mlp_swiglu_combine_fwd_mxfp8")
+def _(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_routed_gate, w_routed_gate_sc, w_shared_up,
+      w_routed_up, w_routed_up_sc, w_shared_down, w_routed_down, w_routed_down_sc, schedule_peer_rank,
+      schedule_peer_token_idx, num_tokens, tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size,
+      minibatch_size):
+    T, H = x.shape
+    I, MB = w_shared_gate.shape[0], macrobatch_size
+    spec = (((H, MB), _FP8), (_sc(H, MB), _U8), ((T, I), _BF16), ((MB, I), _FP8), (_sc(MB, I), _U8), ((T, I), _BF16),
+            ((MB, I), _FP8), (_sc(MB, I), _U8), ((T, I), _BF16), ((I, MB), _FP8), (_sc(I, MB), _U8), ((T, H), _BF16),
+            ((MB, H), _BF16))
+    return tuple(_new(x, s, dt) for s, dt in spec)
+
+
+@_fake("mok::dispatch_mlp_swiglu_combine_bwd_mxfp8")
+def _(d_y_buffer, d_y_buffer_ptrs, d_x_routed_buffer, d_x_routed_buffer_ptrs, router_weight_buffer,
+      router_weight_buffer_ptrs, d_router_weight_buffer, d_router_weight_buffer_ptrs, w_shared_gate, w_routed_gate_T,
+      w_routed_gate_T_sc, w_shared_up, w_routed_up_T, w_routed_up_T_sc, w_shared_down, w_routed_down_T,
+      w_routed_down_T_sc, x_fp8_t_routed, x_sc_t_routed, gate_shared, gate_fp8_routed, gate_sc_routed, up_shared,
+      up_fp8_routed, up_sc_routed, hidden_shared, hidden_fp8_t_routed, hidden_sc_t_routed, x, x_ptrs, w_routed_gate,
+      w_routed_gate_sc, w_routed_up, w_routed_up_sc, schedule_peer_rank, schedule_peer_token_idx, num_tokens,
+      tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+    T, H = x.shape
+    I, El, MB = w_shared_gate.shape[0], w_routed_gate.shape[0], macrobatch_size
+    spec = (((T, H), _BF16), ((MB, H), _BF16), ((T, I), _BF16), ((MB, I), _FP8), (_sc(MB, I), _U8), ((T, I), _BF16),
+            ((MB, I), _FP8), (_sc(MB, I), _U8), ((T, I), _BF16), ((MB, I), _BF16), ((MB, H), _FP8), (_sc(MB, H), _U8),
+            ((I, H), _BF16), ((El, I, H), _BF16), ((I, H), _BF16), ((El, I, H), _BF16), ((H, I), _BF16),
+            ((El, H, I), _BF16))
+    return tuple(_new(x, s, dt) for s, dt in spec)

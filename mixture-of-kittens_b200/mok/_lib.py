@@ -85,6 +85,31 @@ class BwdBf16Args(C.Structure):
     ]
 
 
+def _ptr_struct(name: str, fields: str, ptr_arrays: str) -> type:
+    """A ctypes Structure of `c` (LayerCommon), some uint64* arrays and then plain pointers, in order."""
+    f = [("c", LayerCommon)] + [(n, u64p) for n in ptr_arrays.split()] + [(n, vp) for n in fields.split()]
+    return type(name, (C.Structure,), {"_fields_": f})
+
+
+FwdMxfp8Args = _ptr_struct(
+    "FwdMxfp8Args",
+    "w_shared_gate w_shared_up w_shared_down w_routed_gate_q w_routed_gate_sc w_routed_up_q w_routed_up_sc "
+    "w_routed_down_q w_routed_down_sc x_qt x_sct gate_shared up_shared hidden_shared gate_q gate_sc up_q up_sc "
+    "hidden_qt hidden_sct y_shared y_routed work_x_q work_x_sc work_hidden_q work_hidden_sc",
+    "x_ptrs combine_buffer_ptrs")
+
+BwdMxfp8Args = _ptr_struct(
+    "BwdMxfp8Args",
+    "w_shared_gate w_shared_up w_shared_down w_routed_gate_T_q w_routed_gate_T_sc w_routed_up_T_q w_routed_up_T_sc "
+    "w_routed_down_T_q w_routed_down_T_sc w_routed_gate_q w_routed_gate_sc w_routed_up_q w_routed_up_sc "
+    "x_qt x_sct gate_q gate_sc up_q up_sc hidden_qt hidden_sct gate_shared up_shared hidden_shared "
+    "d_x_shared d_x_routed d_gate_shared d_gate_q d_gate_sc d_up_shared d_up_q d_up_sc d_hidden_shared d_hidden_routed "
+    "d_y_q d_y_sc d_w_shared_gate d_w_shared_up d_w_shared_down d_w_routed_gate d_w_routed_up d_w_routed_down "
+    "work_x_q work_x_sc work_hidden_q work_hidden_sc work_d_y_qt work_d_y_sct work_d_gate_qt work_d_gate_sct "
+    "work_d_up_qt work_d_up_sct router_weights_routed d_router_weight_partials",
+    "d_y_ptrs d_x_routed_buffer_ptrs router_weight_ptrs d_router_weight_ptrs x_ptrs")
+
+
 def _sig(name, restype, argtypes):
     fn = getattr(lib, name)
     fn.restype = restype
@@ -107,6 +132,9 @@ mok_fwd_epilogue = _sig("mok_fwd_epilogue", C.c_int, [vp, vp, vp, vp, C.c_int, C
 mok_bwd_epilogue = _sig("mok_bwd_epilogue", C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp])
 mok_fwd_bf16 = _sig("mok_fwd_bf16", C.c_int, [C.POINTER(FwdBf16Args), vp])
 mok_bwd_bf16 = _sig("mok_bwd_bf16", C.c_int, [C.POINTER(BwdBf16Args), vp])
+mok_fwd_mxfp8 = _sig("mok_fwd_mxfp8", C.c_int, [C.POINTER(FwdMxfp8Args), vp])
+mok_bwd_mxfp8 = _sig("mok_bwd_mxfp8", C.c_int, [C.POINTER(BwdMxfp8Args), vp])
+mok_gemm_mxfp8 = _sig("mok_gemm_mxfp8", C.c_int, [vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp, vp])
 mok_launch_count = _sig("mok_launch_count", C.c_longlong, [])
 mok_profile_enable = _sig("mok_profile_enable", C.c_int, [C.c_int])
 mok_profile_num_slots = _sig("mok_profile_num_slots", C.c_int, [])

@@ -432,3 +432,209 @@ def bwd_epilogue(d_x_shared: Tensor, d_x_routed_buffer: Tensor) -> Tensor:
     _lib.check(_lib.mok_bwd_epilogue(d_x_shared.data_ptr(), d_x_routed_buffer.data_ptr(), out.data_ptr(), T, H,
                                      rows // T, _lib.stream_ptr(d_x_shared.device)), "bwd_epilogue")
     return out
+
+
+# ------------------------------------------------------------------------------------------
+# MXFP8 routed experts  (reference mok/ops.py:194-368 forward, :517-808 backward)
+# ------------------------------------------------------------------------------------------
+def _sc_shape(rows: int, cols: int) -> tuple[int, int, int, int]:
+    return (rows // 128, cols // 128, 32, 16)
+
+
+def _fp8_and_scales(named: dict[str, Tensor]) -> None:
+    for name, t in named.items():
+        want = torch.uint8 if name.endswith("_sc") else torch.float8_e4m3fn
+        _need(t.dtype == want and t.is_contiguous(), f"{name} must be contiguous {want}", TypeError)
+
+
+@torch.library.custom_op("mok::dispatch_mlp_swiglu_combine_fwd_mxfp8", mutates_args=("combine_buffer",))
+def dispatch_mlp_swiglu_combine_fwd_mxfp8(
+    x: Tensor, x_ptrs: list[int], combine_buffer: Tensor, combine_buffer_ptrs: list[int],
+    w_shared_gate: Tensor, w_routed_gate: Tensor, w_routed_gate_sc: Tensor,
+    w_shared_up: Tensor, w_routed_up: Tensor, w_routed_up_sc: Tensor,
+    w_shared_down: Tensor, w_routed_down: Tensor, w_routed_down_sc: Tensor,
+    schedule_peer_rank: Tensor, schedule_peer_token_idx: Tensor, num_tokens: Tensor, tokens_per_expert: Tensor,
+    topk: int, swiglu_limit: float | None, num_comm_sms: int, macrobatch_size: int, minibatch_size: int,
+) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    T, H = _token_hidden(x, "x")
+    _layer_scalars(topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size)
+    ep_size = _pointer_lists({"x_ptrs": x_ptrs, "combine_buffer_ptrs": combine_buffer_ptrs}, "x_ptrs")
+    I = _intermediate(w_shared_gate, H, strict_cols=False)
+    El = _local_experts(w_routed_gate)
+    MB = macrobatch_size
+    cap_probe = schedule_peer_rank.numel() if schedule_peer_rank.ndim == 1 else 0
+    _shapes_and_devices(x.device, [
+        ("combine_buffer", combine_buffer, (T * topk, H)),
+        ("w_shared_gate", w_shared_gate, (I, H)), ("w_routed_gate", w_routed_gate, (El, I, H)),
+        ("w_routed_gate_sc", w_routed_gate_sc, _sc_shape(El * I, H)),
+        ("w_shared_up", w_shared_up, (I, H)), ("w_routed_up", w_routed_up, (El, I, H)),
+        ("w_routed_up_sc", w_routed_up_sc, _sc_shape(El * I, H)),
+        ("w_shared_down", w_shared_down, (H, I)), ("w_routed_down", w_routed_down, (El, H, I)),
+        ("w_routed_down_sc", w_routed_down_sc, _sc_shape(El * H, I)),
+    ], [("schedule_peer_rank", schedule_peer_rank), ("schedule_peer_token_idx", schedule_peer_token_idx),
+        ("num_tokens", num_tokens), ("tokens_per_expert", tokens_per_expert)])
+    cap = _schedule_capacity(schedule_peer_rank)
+    _need(tuple(schedule_peer_token_idx.shape) == (cap,), "schedule_peer_token_idx must have shape (schedule_capacity,)")
+    _need(tuple(num_tokens.shape) == (1,), "num_tokens must have shape (1,)")
+    _need(tuple(tokens_per_expert.shape) == (El,), "tokens_per_expert must have shape (num_local_experts,)")
+    _bf16({"x": x, "combine_buffer": combine_buffer, "w_shared_gate": w_shared_gate, "w_shared_up": w_shared_up,
+           "w_shared_down": w_shared_down})
+    _fp8_and_scales({"w_routed_gate": w_routed_gate, "w_routed_gate_sc": w_routed_gate_sc, "w_routed_up": w_routed_up,
+                     "w_routed_up_sc": w_routed_up_sc, "w_routed_down": w_routed_down,
+                     "w_routed_down_sc": w_routed_down_sc})
+
+    dev = x.device
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    f8 = dict(dtype=torch.float8_e4m3fn, device=dev)
+    u8 = dict(dtype=torch.uint8, device=dev)
+    x_qt, x_sct = torch.empty(H, MB, **f8), torch.empty(_sc_shape(H, MB), **u8)
+    gate_shared, up_shared, hidden_shared = (torch.empty(T, I, **bf) for _ in range(3))
+    gate_q, gate_sc = torch.empty(MB, I, **f8), torch.empty(_sc_shape(MB, I), **u8)
+    up_q, up_sc = torch.empty(MB, I, **f8), torch.empty(_sc_shape(MB, I), **u8)
+    hid_qt, hid_sct = torch.empty(I, MB, **f8), torch.empty(_sc_shape(I, MB), **u8)
+    y_shared, y_routed = torch.empty(T, H, **bf), torch.empty(MB, H, **bf)
+    work = [torch.empty(MB, H, **f8), torch.empty(_sc_shape(MB, H), **u8),
+            torch.empty(MB, I, **f8), torch.empty(_sc_shape(MB, I), **u8)]
+
+    a = _lib.FwdMxfp8Args()
+    a.c = _common(x, ep_size, I, El, topk, cap, MB, minibatch_size, num_comm_sms, swiglu_limit,
+                  (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert))
+    a.c.ep_rank = _own_rank(x, x_ptrs, "x_ptrs")
+    keep = (_lib.ptr_array(x_ptrs), _lib.ptr_array(combine_buffer_ptrs))
+    a.x_ptrs, a.combine_buffer_ptrs = keep
+    fields = dict(
+        w_shared_gate=w_shared_gate, w_shared_up=w_shared_up, w_shared_down=w_shared_down,
+        w_routed_gate_q=w_routed_gate, w_routed_gate_sc=w_routed_gate_sc, w_routed_up_q=w_routed_up,
+        w_routed_up_sc=w_routed_up_sc, w_routed_down_q=w_routed_down, w_routed_down_sc=w_routed_down_sc,
+        x_qt=x_qt, x_sct=x_sct, gate_shared=gate_shared, up_shared=up_shared, hidden_shared=hidden_shared,
+        gate_q=gate_q, gate_sc=gate_sc, up_q=up_q, up_sc=up_sc, hidden_qt=hid_qt, hidden_sct=hid_sct,
+        y_shared=y_shared, y_routed=y_routed, work_x_q=work[0], work_x_sc=work[1], work_hidden_q=work[2],
+        work_hidden_sc=work[3])
+    for k, t in fields.items():
+        setattr(a, k, t.data_ptr())
+    _lib.check(_lib.mok_fwd_mxfp8(a, _lib.stream_ptr(dev)), "dispatch_mlp_swiglu_combine_fwd_mxfp8")
+    return (x_qt, x_sct, gate_shared, gate_q, gate_sc, up_shared, up_q, up_sc, hidden_shared, hid_qt, hid_sct,
+            y_shared, y_routed)
+
+
+@torch.library.custom_op(
+    "mok::dispatch_mlp_swiglu_combine_bwd_mxfp8",
+    mutates_args=("d_x_routed_buffer", "d_router_weight_buffer", "x_fp8_t_routed", "x_sc_t_routed",
+                  "gate_fp8_routed", "gate_sc_routed", "up_fp8_routed", "up_sc_routed",
+                  "hidden_fp8_t_routed", "hidden_sc_t_routed"))
+def dispatch_mlp_swiglu_combine_bwd_mxfp8(
+    d_y_buffer: Tensor, d_y_buffer_ptrs: list[int], d_x_routed_buffer: Tensor, d_x_routed_buffer_ptrs: list[int],
+    router_weight_buffer: Tensor, router_weight_buffer_ptrs: list[int],
+    d_router_weight_buffer: Tensor, d_router_weight_buffer_ptrs: list[int],
+    w_shared_gate: Tensor, w_routed_gate_T: Tensor, w_routed_gate_T_sc: Tensor,
+    w_shared_up: Tensor, w_routed_up_T: Tensor, w_routed_up_T_sc: Tensor,
+    w_shared_down: Tensor, w_routed_down_T: Tensor, w_routed_down_T_sc: Tensor,
+    x_fp8_t_routed: Tensor, x_sc_t_routed: Tensor,
+    gate_shared: Tensor, gate_fp8_routed: Tensor, gate_sc_routed: Tensor,
+    up_shared: Tensor, up_fp8_routed: Tensor, up_sc_routed: Tensor,
+    hidden_shared: Tensor, hidden_fp8_t_routed: Tensor, hidden_sc_t_routed: Tensor,
+    x: Tensor, x_ptrs: list[int],
+    w_routed_gate: Tensor, w_routed_gate_sc: Tensor, w_routed_up: Tensor, w_routed_up_sc: Tensor,
+    schedule_peer_rank: Tensor, schedule_peer_token_idx: Tensor, num_tokens: Tensor, tokens_per_expert: Tensor,
+    topk: int, swiglu_limit: float | None, num_comm_sms: int, macrobatch_size: int, minibatch_size: int,
+) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor,
+           Tensor, Tensor, Tensor, Tensor, Tensor]:
+    T, H = _token_hidden(x, "x")
+    _layer_scalars(topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size)
+    ep_size = _pointer_lists({"x_ptrs": x_ptrs, "d_y_buffer_ptrs": d_y_buffer_ptrs,
+                              "d_x_routed_buffer_ptrs": d_x_routed_buffer_ptrs,
+                              "router_weight_buffer_ptrs": router_weight_buffer_ptrs,
+                              "d_router_weight_buffer_ptrs": d_router_weight_buffer_ptrs}, "x_ptrs")
+    I = _intermediate(w_shared_gate, H, strict_cols=True)
+    El = _local_experts(w_routed_gate)
+    MB = macrobatch_size
+    _shapes_and_devices(x.device, [
+        ("d_y_buffer", d_y_buffer, (T, H)), ("d_x_routed_buffer", d_x_routed_buffer, (T * topk, H)),
+        ("router_weight_buffer", router_weight_buffer, (T, topk)),
+        ("d_router_weight_buffer", d_router_weight_buffer, (T, topk)),
+        ("w_shared_gate", w_shared_gate, (I, H)),
+        ("w_routed_gate_T", w_routed_gate_T, (El, H, I)), ("w_routed_gate_T_sc", w_routed_gate_T_sc, _sc_shape(El * H, I)),
+        ("w_shared_up", w_shared_up, (I, H)),
+        ("w_routed_up_T", w_routed_up_T, (El, H, I)), ("w_routed_up_T_sc", w_routed_up_T_sc, _sc_shape(El * H, I)),
+        ("w_shared_down", w_shared_down, (H, I)),
+        ("w_routed_down_T", w_routed_down_T, (El, I, H)), ("w_routed_down_T_sc", w_routed_down_T_sc, _sc_shape(El * I, H)),
+        ("x_fp8_t_routed", x_fp8_t_routed, (H, MB)), ("x_sc_t_routed", x_sc_t_routed, _sc_shape(H, MB)),
+        ("gate_shared", gate_shared, (T, I)),
+        ("gate_fp8_routed", gate_fp8_routed, (MB, I)), ("gate_sc_routed", gate_sc_routed, _sc_shape(MB, I)),
+        ("up_shared", up_shared, (T, I)),
+        ("up_fp8_routed", up_fp8_routed, (MB, I)), ("up_sc_routed", up_sc_routed, _sc_shape(MB, I)),
+        ("hidden_shared", hidden_shared, (T, I)),
+        ("hidden_fp8_t_routed", hidden_fp8_t_routed, (I, MB)), ("hidden_sc_t_routed", hidden_sc_t_routed, _sc_shape(I, MB)),
+        ("w_routed_gate", w_routed_gate, (El, I, H)), ("w_routed_gate_sc", w_routed_gate_sc, _sc_shape(El * I, H)),
+        ("w_routed_up", w_routed_up, (El, I, H)), ("w_routed_up_sc", w_routed_up_sc, _sc_shape(El * I, H)),
+    ], [("schedule_peer_rank", schedule_peer_rank), ("schedule_peer_token_idx", schedule_peer_token_idx),
+        ("num_tokens", num_tokens), ("tokens_per_expert", tokens_per_expert)])
+    cap = _schedule_capacity(schedule_peer_rank)
+    _need(tuple(schedule_peer_token_idx.shape) == (cap,), "schedule_peer_token_idx must have shape (schedule_capacity,)")
+    _need(tuple(num_tokens.shape) == (1,), "num_tokens must have shape (1,)")
+    _need(tuple(tokens_per_expert.shape) == (El,), "tokens_per_expert must have shape (num_local_experts,)")
+    _bf16({"x": x, "d_y_buffer": d_y_buffer, "d_x_routed_buffer": d_x_routed_buffer, "w_shared_gate": w_shared_gate,
+           "w_shared_up": w_shared_up, "w_shared_down": w_shared_down, "gate_shared": gate_shared,
+           "up_shared": up_shared, "hidden_shared": hidden_shared})
+    _fp8_and_scales({"w_routed_gate_T": w_routed_gate_T, "w_routed_gate_T_sc": w_routed_gate_T_sc,
+                     "w_routed_up_T": w_routed_up_T, "w_routed_up_T_sc": w_routed_up_T_sc,
+                     "w_routed_down_T": w_routed_down_T, "w_routed_down_T_sc": w_routed_down_T_sc,
+                     "x_fp8_t_routed": x_fp8_t_routed, "x_sc_t_routed_sc": x_sc_t_routed,
+                     "gate_fp8_routed": gate_fp8_routed, "gate_sc_routed_sc": gate_sc_routed,
+                     "up_fp8_routed": up_fp8_routed, "up_sc_routed_sc": up_sc_routed,
+                     "hidden_fp8_t_routed": hidden_fp8_t_routed, "hidden_sc_t_routed_sc": hidden_sc_t_routed,
+                     "w_routed_gate": w_routed_gate, "w_routed_gate_sc": w_routed_gate_sc,
+                     "w_routed_up": w_routed_up, "w_routed_up_sc": w_routed_up_sc})
+    for name, t in (("router_weight_buffer", router_weight_buffer), ("d_router_weight_buffer", d_router_weight_buffer)):
+        _need(t.dtype == torch.float32 and t.is_contiguous(), f"{name} must be contiguous float32", TypeError)
+
+    dev = x.device
+    bf = dict(dtype=torch.bfloat16, device=dev)
+    f8 = dict(dtype=torch.float8_e4m3fn, device=dev)
+    u8 = dict(dtype=torch.uint8, device=dev)
+    d_x_shared, d_x_routed = torch.empty(T, H, **bf), torch.empty(MB, H, **bf)
+    d_gate_shared, d_up_shared, d_hidden_shared = (torch.empty(T, I, **bf) for _ in range(3))
+    d_gate_q, d_gate_sc = torch.empty(MB, I, **f8), torch.empty(_sc_shape(MB, I), **u8)
+    d_up_q, d_up_sc = torch.empty(MB, I, **f8), torch.empty(_sc_shape(MB, I), **u8)
+    d_hidden_routed = torch.empty(MB, I, **bf)
+    d_y_q, d_y_sc = torch.empty(MB, H, **f8), torch.empty(_sc_shape(MB, H), **u8)
+    d_w_shared_gate, d_w_shared_up, d_w_shared_down = torch.empty(I, H, **bf), torch.empty(I, H, **bf), torch.empty(H, I, **bf)
+    d_w_routed_gate, d_w_routed_up = torch.empty(El, I, H, **bf), torch.empty(El, I, H, **bf)
+    d_w_routed_down = torch.empty(El, H, I, **bf)
+    work = dict(
+        work_x_q=torch.empty(MB, H, **f8), work_x_sc=torch.empty(_sc_shape(MB, H), **u8),
+        work_hidden_q=torch.empty(MB, I, **f8), work_hidden_sc=torch.empty(_sc_shape(MB, I), **u8),
+        work_d_y_qt=torch.empty(H, MB, **f8), work_d_y_sct=torch.empty(_sc_shape(H, MB), **u8),
+        work_d_gate_qt=torch.empty(I, MB, **f8), work_d_gate_sct=torch.empty(_sc_shape(I, MB), **u8),
+        work_d_up_qt=torch.empty(I, MB, **f8), work_d_up_sct=torch.empty(_sc_shape(I, MB), **u8),
+        router_weights_routed=torch.empty(MB, dtype=torch.float32, device=dev),
+        d_router_weight_partials=torch.empty(MB, I // 256, dtype=torch.float32, device=dev))
+
+    a = _lib.BwdMxfp8Args()
+    a.c = _common(x, ep_size, I, El, topk, cap, MB, minibatch_size, num_comm_sms, swiglu_limit,
+                  (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert))
+    a.c.ep_rank = _own_rank(x, x_ptrs, "x_ptrs")
+    keep = [_lib.ptr_array(p) for p in (d_y_buffer_ptrs, d_x_routed_buffer_ptrs, router_weight_buffer_ptrs,
+                                        d_router_weight_buffer_ptrs, x_ptrs)]
+    a.d_y_ptrs, a.d_x_routed_buffer_ptrs, a.router_weight_ptrs, a.d_router_weight_ptrs, a.x_ptrs = keep
+    fields = dict(
+        w_shared_gate=w_shared_gate, w_shared_up=w_shared_up, w_shared_down=w_shared_down,
+        w_routed_gate_T_q=w_routed_gate_T, w_routed_gate_T_sc=w_routed_gate_T_sc,
+        w_routed_up_T_q=w_routed_up_T, w_routed_up_T_sc=w_routed_up_T_sc,
+        w_routed_down_T_q=w_routed_down_T, w_routed_down_T_sc=w_routed_down_T_sc,
+        w_routed_gate_q=w_routed_gate, w_routed_gate_sc=w_routed_gate_sc,
+        w_routed_up_q=w_routed_up, w_routed_up_sc=w_routed_up_sc,
+        x_qt=x_fp8_t_routed, x_sct=x_sc_t_routed, gate_q=gate_fp8_routed, gate_sc=gate_sc_routed,
+        up_q=up_fp8_routed, up_sc=up_sc_routed, hidden_qt=hidden_fp8_t_routed, hidden_sct=hidden_sc_t_routed,
+        gate_shared=gate_shared, up_shared=up_shared, hidden_shared=hidden_shared,
+        d_x_shared=d_x_shared, d_x_routed=d_x_routed, d_gate_shared=d_gate_shared, d_gate_q=d_gate_q,
+        d_gate_sc=d_gate_sc, d_up_shared=d_up_shared, d_up_q=d_up_q, d_up_sc=d_up_sc,
+        d_hidden_shared=d_hidden_shared, d_hidden_routed=d_hidden_routed, d_y_q=d_y_q, d_y_sc=d_y_sc,
+        d_w_shared_gate=d_w_shared_gate, d_w_shared_up=d_w_shared_up, d_w_shared_down=d_w_shared_down,
+        d_w_routed_gate=d_w_routed_gate, d_w_routed_up=d_w_routed_up, d_w_routed_down=d_w_routed_down, **work)
+    for k, t in fields.items():
+        setattr(a, k, t.data_ptr())
+    _lib.check(_lib.mok_bwd_mxfp8(a, _lib.stream_ptr(dev)), "dispatch_mlp_swiglu_combine_bwd_mxfp8")
+    return (d_x_shared, d_x_routed, d_gate_shared, d_gate_q, d_gate_sc, d_up_shared, d_up_q, d_up_sc,
+            d_hidden_shared, d_hidden_routed, d_y_q, d_y_sc, d_w_shared_gate, d_w_routed_gate, d_w_shared_up,
+            d_w_routed_up, d_w_shared_down, d_w_routed_down)

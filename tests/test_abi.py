@@ -44,7 +44,7 @@ def test_struct_sizes_match_header():
     import subprocess
     import tempfile
     import mok
-    src = '#include <stdio.h>\n#include "mok_b200.h"\nint main(){printf("%zu %zu %zu", sizeof(mok_layer_common), sizeof(mok_fwd_bf16_args), sizeof(mok_bwd_bf16_args));return 0;}\n'
+    src = '#include <stdio.h>\n#include "mok_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu", sizeof(mok_layer_common), sizeof(mok_fwd_bf16_args), sizeof(mok_bwd_bf16_args), sizeof(mok_fwd_mxfp8_args), sizeof(mok_bwd_mxfp8_args));return 0;}\n'
     with tempfile.TemporaryDirectory() as d:
         c = os.path.join(d, "s.c")
         open(c, "w").write(src)
@@ -52,4 +52,21 @@ def test_struct_sizes_match_header():
         subprocess.check_call(["gcc", "-I", os.path.join(ROOT, "include"), c, "-o", exe])
         sizes = [int(v) for v in subprocess.check_output([exe]).split()]
     L = mok._lib
-    assert sizes == [ctypes.sizeof(L.LayerCommon), ctypes.sizeof(L.FwdBf16Args), ctypes.sizeof(L.BwdBf16Args)]
+    assert sizes == [ctypes.sizeof(L.LayerCommon), ctypes.sizeof(L.FwdBf16Args), ctypes.sizeof(L.BwdBf16Args),
+                     ctypes.sizeof(L.FwdMxfp8Args), ctypes.sizeof(L.BwdMxfp8Args)]
+
+
+def test_ctypes_field_order_matches_header():
+    """Same sizes are not enough: every struct member must sit where the header puts it."""
+    import mok
+    L = mok._lib
+    text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "mok_b200.h")).read(), flags=re.S)
+    pairs = (("mok_layer_common", L.LayerCommon), ("mok_fwd_bf16_args", L.FwdBf16Args),
+             ("mok_bwd_bf16_args", L.BwdBf16Args), ("mok_fwd_mxfp8_args", L.FwdMxfp8Args),
+             ("mok_bwd_mxfp8_args", L.BwdMxfp8Args))
+    type_words = {"const", "void", "uint64_t", "int32_t", "int", "float", "mok_layer_common"}
+    for cname, struct in pairs:
+        body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, re.S).group(1)
+        names = [w for decl in body.split(";") for w in decl.replace("*", " ").replace(",", " ").split()
+                 if w not in type_words]
+        assert names == [f[0] for f in struct._fields_], cname

@@ -183,3 +183,27 @@ def test_gemm_bf16_layouts(cuda_device, a_mn, b_mn, m, n, k):
     assert mok.last_status(cuda_device)[0] == 0
     assert torch.isfinite(c.float()).all()
     assert rel_l2(ref, c.float()) < 4e-3
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 512, 512), (1024, 768, 2048), (384, 256, 7168)])
+def test_gemm_mxfp8(cuda_device, m, n, k):
+    """Block-scaled tcgen05 GEMM: operands quantised by ops.mxfp8_quantize (bit-exact, tested above),
+    result compared with an fp32 matmul of the dequantised operands."""
+    mok = _mok()
+    L = mok._lib
+    g = torch.Generator().manual_seed(m + n + k)
+    a = (torch.randn(m, k, generator=g) * torch.exp(torch.randn(m, 1, generator=g))).to(torch.bfloat16)
+    b = (torch.randn(n, k, generator=g) * torch.exp(torch.randn(n, 1, generator=g))).to(torch.bfloat16)
+    aq, asc, _, _ = mok.ops.mxfp8_quantize(a.to(cuda_device), True, False)
+    bq, bsc, _, _ = mok.ops.mxfp8_quantize(b.to(cuda_device), True, False)
+    a_dq = torch.from_numpy(O.mxfp8_dequantize(to_bytes(aq).reshape(m, k), asc.cpu().numpy()))
+    b_dq = torch.from_numpy(O.mxfp8_dequantize(to_bytes(bq).reshape(n, k), bsc.cpu().numpy()))
+    ref = a_dq @ b_dq.T
+    c = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=cuda_device)
+    mok.last_status(cuda_device, clear=True)
+    L.check(L.mok_gemm_mxfp8(aq.data_ptr(), asc.data_ptr(), bq.data_ptr(), bsc.data_ptr(), c.data_ptr(), m, n, k,
+                             L.status_tensor(cuda_device).data_ptr(), L.stream_ptr(cuda_device)), "gemm_mxfp8")
+    torch.cuda.synchronize()
+    assert mok.last_status(cuda_device)[0] == 0
+    assert torch.isfinite(c.float()).all()
+    assert rel_l2(ref, c.float()) < 4e-3
