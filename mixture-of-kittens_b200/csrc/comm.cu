@@ -108,13 +108,15 @@ __global__ void __launch_bounds__(256) epilogue_kernel(const uint4* __restrict__
 template <bool kScale>
 __global__ void __launch_bounds__(256) dispatch_rows_kernel(RowMoveParams p) {
     const int n_total = min(*p.num_tokens, p.capacity);
-    const int rows = max(0, min(n_total - p.row_offset, p.row_limit));
+    const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
+    int row_lo, rows;
+    chunk_range(win_rows, p.chunk, row_lo, rows);
     const int warps_per_block = blockDim.x >> 5;
     const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     const int n_warps = gridDim.x * warps_per_block;
     const int vec_per_row = p.hidden >> 3;
-    for (int row = warp; row < rows; row += n_warps) {
+    for (int row = row_lo + warp; row < rows; row += n_warps) {
         const int g = p.row_offset + row;
         const int pr = p.peer_rank[g];
         uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.local) + static_cast<size_t>(row) * p.hidden);
@@ -160,13 +162,15 @@ __global__ void __launch_bounds__(256) dispatch_rows_kernel(RowMoveParams p) {
 // the float at peer[...]'s d_router_weight[peer_token_idx[i]].
 __global__ void __launch_bounds__(256) combine_rows_kernel(RowMoveParams p) {
     const int n_total = min(*p.num_tokens, p.capacity);
-    const int rows = max(0, min(n_total - p.row_offset, p.row_limit));
+    const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
+    int row_lo, rows;
+    chunk_range(win_rows, p.chunk, row_lo, rows);
     const int warps_per_block = blockDim.x >> 5;
     const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     const int n_warps = gridDim.x * warps_per_block;
     const int vec_per_row = p.hidden >> 3;
-    for (int row = warp; row < rows; row += n_warps) {
+    for (int row = row_lo + warp; row < rows; row += n_warps) {
         const int g = p.row_offset + row;
         const int pr = p.peer_rank[g];
         if (pr < 0) continue;
@@ -199,13 +203,15 @@ __global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, Qu
     constexpr int kCols = 256, kStride = kCols + 8;
     __shared__ __align__(16) __nv_bfloat16 tile[32 * kStride];
     const int n_total = min(*p.num_tokens, p.capacity);
-    const int rows = max(0, min(n_total - p.row_offset, p.row_limit));
+    const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
+    int row_lo, row_hi;
+    chunk_range(win_rows, p.chunk, row_lo, row_hi);
     const int col_chunks = p.hidden / kCols;
-    const int units = (rows / 32) * col_chunks;
+    const int units = ((row_hi - row_lo) / 32) * col_chunks;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
         const int rb = unit / col_chunks, cc = unit - rb * col_chunks;
-        const int row0 = rb * 32, col0 = cc * kCols;
+        const int row0 = row_lo + rb * 32, col0 = cc * kCols;
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
             const int r = warp * 4 + i;

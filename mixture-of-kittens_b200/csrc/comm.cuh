@@ -19,6 +19,7 @@ struct RowMoveParams {
     int capacity;
     int row_offset;            // first schedule row of this macrobatch
     int row_limit;             // macrobatch size
+    ChunkSpec chunk;           // row sub-range of the window this launch covers
     int hidden;
     int row_divisor;           // dispatch: topk (route -> token row); 1 otherwise
     float* row_scale_out;      // dispatch<scale>: [row_limit] router weight of every routed row

@@ -208,6 +208,21 @@ __device__ __forceinline__ float bf16_round(float x) {
     return __bfloat162float(__float2bfloat16_rn(x));
 }
 
+// A window of `win_rows` schedule rows (known only on the device) is cut into `num_chunks` row ranges
+// of equal size, a multiple of 256 and at least `min_rows` (the minibatch size), so that the
+// host can enqueue a fixed number of launches per window and overlap the row movement of one
+// chunk with the GEMMs of another.  num_chunks <= 1 selects the whole window.
+struct ChunkSpec {
+    int index, num_chunks, min_rows;
+};
+__device__ __forceinline__ void chunk_range(int win_rows, const ChunkSpec& c, int& lo, int& hi) {
+    if (c.num_chunks <= 1) { lo = 0; hi = win_rows; return; }
+    int per = (win_rows + c.num_chunks - 1) / c.num_chunks;
+    per = max((per + 255) / 256 * 256, c.min_rows);
+    lo = min(win_rows, c.index * per);
+    hi = (c.index == c.num_chunks - 1) ? win_rows : min(win_rows, lo + per);
+}
+
 #define MOK_CUDA_CHECK(expr)                                       \
     do {                                                           \
         cudaError_t err__ = (expr);                                \

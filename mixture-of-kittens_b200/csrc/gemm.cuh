@@ -47,6 +47,7 @@ struct GemmParams {
     int row_limit;                 // window size in rows; buffers are indexed relative to the window
     const int* tokens_per_expert;  // nullptr -> one group covering every row
     int num_experts;
+    ChunkSpec chunk;               // row sub-range of the window this launch covers (not used by weight gradients)
     // tiling
     int n_tiles;                   // output tiles along N
     int m_tiles_w;                 // weight-gradient mode: output tiles along M
@@ -121,8 +122,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     const int n_total = p.num_tokens ? min(*p.num_tokens, p.capacity) : p.rows_host;
     const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
     // a weight-gradient launch that only accumulates has nothing to do on an empty window
+    int chunk_lo = 0, chunk_hi = win_rows;
+    if (!kWgrad) chunk_range(win_rows, p.chunk, chunk_lo, chunk_hi);
+    const int m_tile0 = chunk_lo / kBlockM;
     const int num_tiles = kWgrad ? ((p.accumulate && win_rows == 0) ? 0 : E * p.m_tiles_w * p.n_tiles)
-                                 : (win_rows / kBlockM) * p.n_tiles;
+                                 : ((chunk_hi - chunk_lo) / kBlockM) * p.n_tiles;
 
     // tile -> coordinates.  a_row: first A/C row (window-relative); k_row0/k_blocks: contraction range
     auto decode = [&](int tile, int& m_idx, int& n_idx, int& expert, int& k_row0, int& k_blocks) {
@@ -138,8 +142,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             k_row0 = lo - p.row_offset;
             k_blocks = hi > lo ? (hi - lo) / kBlockK : 0;
         } else {
-            m_idx = tile / p.n_tiles;
-            n_idx = tile - m_idx * p.n_tiles;
+            const int m_rel = tile / p.n_tiles;
+            n_idx = tile - m_rel * p.n_tiles;
+            m_idx = m_tile0 + m_rel;
             expert = 0;
             if (p.tokens_per_expert) {
                 const int g = p.row_offset + m_idx * kBlockM;

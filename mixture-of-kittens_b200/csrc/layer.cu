@@ -9,6 +9,10 @@
 // Backward, per window (first window first; later windows replay dispatch + gate/up):
 //   reverse-combine (w * d_y)  ->  [dgrad down + SwiGLU backward + router-grad partials]
 //   ->  dgrad gate+up (one accumulator)  ->  reverse-dispatch (+ router grads)  ->  3 wgrads
+#include <cstdlib>
+#include <mutex>
+#include <vector>
+
 #include "comm.cuh"
 #include "gemm.cuh"
 #include "mxgemm.cuh"
@@ -41,8 +45,12 @@ int fill_peers(PeerPtrs& out, const uint64_t* ptrs, int W) {
     return MOK_OK;
 }
 
+// row sub-range the helpers below put into every routed launch they build (set by the pipeline)
+thread_local ChunkSpec t_chunk = {0, 1, 0};
+
 GemmParams base_params(const mok_layer_common& c, bool routed, int off, int limit) {
     GemmParams p{};
+    if (routed) p.chunk = t_chunk;
     if (routed) {
         p.num_tokens = c.num_tokens;
         p.capacity = c.schedule_capacity;
@@ -173,7 +181,133 @@ RowMoveParams row_move(const mok_layer_common& c, const Dims& d, int off, int li
     r.row_limit = limit;
     r.hidden = d.H;
     r.row_divisor = 1;
+    r.chunk = t_chunk;
     return r;
+}
+
+}  // namespace
+}  // namespace mok
+
+// -------------------------------------------------------------------------------------------------
+// Two-stream pipeline.  A window is cut into `chunks` row ranges (derived on the device from
+// num_tokens, see chunk_range); the row movement of a chunk runs on a side stream while the GEMMs
+// of its neighbours run on the caller's stream:
+//     side:  load(0) load(1)        store(0) load(2)        store(1) ...
+//     main:          compute(0)              compute(1)              ...
+// Dependencies are CUDA events only (no kernel waits on another kernel), the side stream forks from
+// and joins back into the caller's stream inside the call, and results do not depend on timing.
+// The movement kernels are small-footprint CTAs that share SMs with the persistent GEMM CTAs.
+// -------------------------------------------------------------------------------------------------
+namespace mok {
+namespace {
+
+struct DeviceStreams {
+    cudaStream_t side = nullptr;
+    std::vector<cudaEvent_t> events;
+};
+DeviceStreams g_streams[64];
+std::mutex g_streams_mu;
+
+class Pipeline {
+public:
+    Pipeline(cudaStream_t main, int chunks, int min_rows) : main_(main), chunks_(chunks), min_rows_(min_rows) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { rc_ = MOK_ERR_CUDA; return; }
+        ds_ = &g_streams[dev];
+        std::lock_guard<std::mutex> lock(g_streams_mu);
+        if (chunks_ > 1 && ds_->side == nullptr) {
+            int lo = 0, hi = 0;
+            cudaDeviceGetStreamPriorityRange(&lo, &hi);
+            if (cudaStreamCreateWithPriority(&ds_->side, cudaStreamNonBlocking, hi) != cudaSuccess) rc_ = MOK_ERR_CUDA;
+        }
+    }
+    int chunks() const { return chunks_; }
+    cudaStream_t main() const { return main_; }
+    cudaStream_t side() const { return chunks_ > 1 ? ds_->side : main_; }
+    int error() const { return rc_; }
+
+    // side stream continues after everything enqueued on main so far / main after side
+    int fork() { return chunks_ > 1 ? order(main_, ds_->side) : MOK_OK; }
+    int join() { return chunks_ > 1 ? order(ds_->side, main_) : MOK_OK; }
+
+    // load(c) and store(c) are enqueued on side(), compute(c) on main(); t_chunk selects chunk c
+    // Only window 0 is cut into chunks: later windows hold rows only when the schedule exceeds one
+    // macrobatch, and an empty launch is cheaper than eight of them.
+    template <class Load, class Compute, class Store>
+    int run(bool chunked, Load load, Compute compute, Store store) {
+        if (rc_ != MOK_OK) return rc_;
+        if (chunks_ <= 1 || !chunked) {
+            t_chunk = ChunkSpec{0, 1, 0};
+            int rc;
+            if ((rc = load(main_))) return rc;
+            if ((rc = compute(main_))) return rc;
+            return store(main_);
+        }
+        int rc = MOK_OK;
+        std::vector<cudaEvent_t> loaded(chunks_);
+        set_chunk(0);
+        if ((rc = load(ds_->side))) return finish(rc);
+        if ((rc = record(ds_->side, loaded[0]))) return finish(rc);
+        for (int c = 0; c < chunks_ && rc == MOK_OK; ++c) {
+            if (c + 1 < chunks_) {
+                set_chunk(c + 1);
+                if ((rc = load(ds_->side))) break;
+                if ((rc = record(ds_->side, loaded[c + 1]))) break;
+            }
+            set_chunk(c);
+            if (cudaStreamWaitEvent(main_, loaded[c], 0) != cudaSuccess) { rc = MOK_ERR_CUDA; break; }
+            if ((rc = compute(main_))) break;
+            cudaEvent_t computed;
+            if ((rc = record(main_, computed))) break;
+            if (cudaStreamWaitEvent(ds_->side, computed, 0) != cudaSuccess) { rc = MOK_ERR_CUDA; break; }
+            if ((rc = store(ds_->side))) break;
+        }
+        return finish(rc);
+    }
+
+private:
+    void set_chunk(int c) { t_chunk = ChunkSpec{c, chunks_, min_rows_}; }
+    int finish(int rc) { t_chunk = ChunkSpec{0, 1, 0}; return rc; }
+    int record(cudaStream_t s, cudaEvent_t& out) {
+        std::lock_guard<std::mutex> lock(g_streams_mu);
+        if (next_ == ds_->events.size()) {
+            cudaEvent_t e = nullptr;
+            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return MOK_ERR_CUDA;
+            ds_->events.push_back(e);
+        }
+        out = ds_->events[next_++];
+        return cudaEventRecord(out, s) == cudaSuccess ? MOK_OK : MOK_ERR_CUDA;
+    }
+    int order(cudaStream_t first, cudaStream_t then) {
+        cudaEvent_t e;
+        int rc = record(first, e);
+        if (rc) return rc;
+        return cudaStreamWaitEvent(then, e, 0) == cudaSuccess ? MOK_OK : MOK_ERR_CUDA;
+    }
+    cudaStream_t main_;
+    int chunks_, min_rows_;
+    DeviceStreams* ds_ = nullptr;
+    size_t next_ = 0;
+    int rc_ = MOK_OK;
+};
+
+// CTAs of a row-movement launch.  Inside the pipeline they share the SMs with the persistent GEMM CTAs.
+int move_grid() {
+    static const int configured = [] {
+        const char* e = std::getenv("MOK_B200_COMM_BLOCKS");
+        return e ? std::atoi(e) : 0;
+    }();
+    return configured > 0 ? configured : device_sm_count() * 2;
+}
+
+int pipeline_chunks(const mok_layer_common& c, int limit) {
+    static const int configured = [] {
+        const char* e = std::getenv("MOK_B200_CHUNKS");
+        const int v = e ? std::atoi(e) : 8;
+        return v < 1 ? 1 : (v > 32 ? 32 : v);
+    }();
+    const int by_minibatch = limit / c.minibatch_size;
+    return std::max(1, std::min(configured, by_minibatch));
 }
 
 }  // namespace
@@ -191,9 +325,12 @@ extern "C" int mok_fwd_bf16(const mok_fwd_bf16_args* a, void* stream) {
     MOK_TRY(fill_peers(x_peers, a->x_ptrs, d.W));
     MOK_TRY(fill_peers(combine_peers, a->combine_buffer_ptrs, d.W));
     const void* x_local = x_peers.p[d.rank];
-    const int move_blocks = device_sm_count() * 4;
+    const int move_blocks = move_grid();
+    Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
+    MOK_TRY(pipe.error());
+    MOK_TRY(pipe.fork());
 
-    // shared expert on the local tokens
+    // shared expert on the local tokens (overlaps the first dispatch chunk)
     MOK_TRY(run_gate_up(c, d, false, 0, d.T, x_local, d.T, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
                         a->hidden_shared, s));
     MOK_TRY(run_down(c, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
@@ -202,16 +339,25 @@ extern "C" int mok_fwd_bf16(const mok_fwd_bf16_args* a, void* stream) {
     for (int m = n_macro - 1; m >= 0; --m) {
         const int off = m * d.MB;
         const int limit = std::min(d.MB, d.cap - off);
-        RowMoveParams disp = row_move(c, d, off, limit, a->x_routed);
-        disp.peers = x_peers;
-        disp.row_divisor = d.K;
-        MOK_TRY(launch_dispatch_rows(disp, false, move_blocks, s));
-        MOK_TRY(run_gate_up(c, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up, a->gate_routed,
-                            a->up_routed, a->hidden_routed, s));
-        MOK_TRY(run_down(c, d, true, off, limit, a->hidden_routed, d.MB, a->w_routed_down, a->y_routed, s));
-        RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
-        comb.peers = combine_peers;
-        MOK_TRY(launch_combine_rows(comb, move_blocks, s));
+        MOK_TRY(pipe.run(m == 0,
+            [&](cudaStream_t st) {
+                RowMoveParams disp = row_move(c, d, off, limit, a->x_routed);
+                disp.peers = x_peers;
+                disp.row_divisor = d.K;
+                return launch_dispatch_rows(disp, false, move_blocks, st);
+            },
+            [&](cudaStream_t st) {
+                MOK_TRY(run_gate_up(c, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up,
+                                    a->gate_routed, a->up_routed, a->hidden_routed, st));
+                return run_down(c, d, true, off, limit, a->hidden_routed, d.MB, a->w_routed_down, a->y_routed, st);
+            },
+            [&](cudaStream_t st) {
+                RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
+                comb.peers = combine_peers;
+                return launch_combine_rows(comb, move_blocks, st);
+            }));
+        MOK_TRY(pipe.join());      // the next window reuses the buffers
+        if (m > 0) MOK_TRY(pipe.fork());
     }
     return MOK_OK;
 }
@@ -231,10 +377,13 @@ extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
     if (!a->router_weights_routed || !a->d_router_weight_partials) return MOK_ERR_INVALID;
     const void* dy_local = dy_peers.p[d.rank];
     const void* x_local = x_peers.p[d.rank];
-    const int move_blocks = device_sm_count() * 4;
+    const int move_blocks = move_grid();
     const int partial_cols = d.I / kBlockN;
+    Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
+    MOK_TRY(pipe.error());
+    MOK_TRY(pipe.fork());
 
-    // shared expert
+    // shared expert (overlaps the first reverse-combine chunk)
     MOK_TRY(run_dgrad_down(c, d, false, 0, d.T, dy_local, d.T, a->w_shared_down, a->gate_shared, a->up_shared,
                            a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, nullptr, s));
     MOK_TRY(run_dgrad_gate_up(c, d, false, 0, d.T, a->d_gate_shared, a->d_up_shared, d.T, a->w_shared_gate, a->w_shared_up,
@@ -254,24 +403,33 @@ extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
             MOK_TRY(launch_dispatch_rows(disp, false, move_blocks, s));
             MOK_TRY(run_gate_up(c, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up, a->gate_routed,
                                 a->up_routed, a->hidden_routed, s));
+            MOK_TRY(pipe.fork());
         }
-        RowMoveParams rc = row_move(c, d, off, limit, a->d_y_routed);
-        rc.peers = dy_peers;
-        rc.scale_peers = rw_peers;
-        rc.row_divisor = d.K;
-        rc.row_scale_out = a->router_weights_routed;
-        MOK_TRY(launch_dispatch_rows(rc, true, move_blocks, s));
-        MOK_TRY(run_dgrad_down(c, d, true, off, limit, a->d_y_routed, d.MB, a->w_routed_down, a->gate_routed, a->up_routed,
-                               a->d_hidden_routed, a->d_gate_routed, a->d_up_routed, a->router_weights_routed,
-                               a->d_router_weight_partials, s));
-        MOK_TRY(run_dgrad_gate_up(c, d, true, off, limit, a->d_gate_routed, a->d_up_routed, d.MB, a->w_routed_gate,
-                                  a->w_routed_up, a->d_x_routed, s));
-        RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
-        rd.peers = dxr_peers;
-        rd.scale_peers = drw_peers;
-        rd.partials = a->d_router_weight_partials;
-        rd.partial_cols = partial_cols;
-        MOK_TRY(launch_combine_rows(rd, move_blocks, s));
+        MOK_TRY(pipe.run(m == 0,
+            [&](cudaStream_t st) {
+                RowMoveParams rc = row_move(c, d, off, limit, a->d_y_routed);
+                rc.peers = dy_peers;
+                rc.scale_peers = rw_peers;
+                rc.row_divisor = d.K;
+                rc.row_scale_out = a->router_weights_routed;
+                return launch_dispatch_rows(rc, true, move_blocks, st);
+            },
+            [&](cudaStream_t st) {
+                MOK_TRY(run_dgrad_down(c, d, true, off, limit, a->d_y_routed, d.MB, a->w_routed_down, a->gate_routed,
+                                       a->up_routed, a->d_hidden_routed, a->d_gate_routed, a->d_up_routed,
+                                       a->router_weights_routed, a->d_router_weight_partials, st));
+                return run_dgrad_gate_up(c, d, true, off, limit, a->d_gate_routed, a->d_up_routed, d.MB, a->w_routed_gate,
+                                         a->w_routed_up, a->d_x_routed, st);
+            },
+            [&](cudaStream_t st) {
+                RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
+                rd.peers = dxr_peers;
+                rd.scale_peers = drw_peers;
+                rd.partials = a->d_router_weight_partials;
+                rd.partial_cols = partial_cols;
+                return launch_combine_rows(rd, move_blocks, st);
+            }));
+        MOK_TRY(pipe.join());
         const int acc = m > 0 ? 1 : 0;
         MOK_TRY(run_wgrad(c, true, off, limit, a->d_y_routed, d.H, a->hidden_routed, d.I, d.MB, a->d_w_routed_down, acc, s));
         MOK_TRY(run_wgrad(c, true, off, limit, a->d_gate_routed, d.I, a->x_routed, d.H, d.MB, a->d_w_routed_gate, acc, s));
@@ -309,6 +467,7 @@ namespace {
 
 MxGemmParams mx_base(const mok_layer_common& c, int off, int limit) {
     MxGemmParams p{};
+    p.chunk = t_chunk;
     p.num_tokens = c.num_tokens;
     p.capacity = c.schedule_capacity;
     p.tokens_per_expert = c.tokens_per_expert;
@@ -388,14 +547,16 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
     if (!a) return MOK_ERR_INVALID;
     Dims d;
     MOK_TRY(check_common(a->c, d));
-    if (d.MB % 128 || d.H % 128 || d.I % 128) return MOK_ERR_INVALID;
     const mok_layer_common& c = a->c;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     PeerPtrs x_peers{}, combine_peers{};
     MOK_TRY(fill_peers(x_peers, a->x_ptrs, d.W));
     MOK_TRY(fill_peers(combine_peers, a->combine_buffer_ptrs, d.W));
     const void* x_local = x_peers.p[d.rank];
-    const int move_blocks = device_sm_count() * 4;
+    const int move_blocks = move_grid();
+    Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
+    MOK_TRY(pipe.error());
+    MOK_TRY(pipe.fork());
 
     MOK_TRY(run_gate_up(c, d, false, 0, d.T, x_local, d.T, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
                         a->hidden_shared, s));
@@ -405,19 +566,28 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
     for (int m = n_macro - 1; m >= 0; --m) {
         const int off = m * d.MB;
         const int limit = std::min(d.MB, d.cap - off);
-        RowMoveParams disp = row_move(c, d, off, limit, nullptr);
-        disp.peers = x_peers;
-        disp.row_divisor = d.K;
-        QuantOut xo{u8(a->work_x_q), u8(a->work_x_sc), u8(a->x_qt), u8(a->x_sct), d.MB};
-        MOK_TRY(launch_dispatch_quant(disp, xo, false, move_blocks, s));
-        MOK_TRY(mx_gate_up(c, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
-                           a->w_routed_up_q, a->w_routed_up_sc, a->gate_q, a->gate_sc, a->up_q, a->up_sc, a->work_hidden_q,
-                           a->work_hidden_sc, a->hidden_qt, a->hidden_sct, s));
-        MOK_TRY(mx_down(c, d, off, limit, a->work_hidden_q, a->work_hidden_sc, a->w_routed_down_q, a->w_routed_down_sc,
-                        a->y_routed, s));
-        RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
-        comb.peers = combine_peers;
-        MOK_TRY(launch_combine_rows(comb, move_blocks, s));
+        MOK_TRY(pipe.run(m == 0,
+            [&](cudaStream_t st) {
+                RowMoveParams disp = row_move(c, d, off, limit, nullptr);
+                disp.peers = x_peers;
+                disp.row_divisor = d.K;
+                QuantOut xo{u8(a->work_x_q), u8(a->work_x_sc), u8(a->x_qt), u8(a->x_sct), d.MB};
+                return launch_dispatch_quant(disp, xo, false, move_blocks, st);
+            },
+            [&](cudaStream_t st) {
+                MOK_TRY(mx_gate_up(c, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
+                                   a->w_routed_up_q, a->w_routed_up_sc, a->gate_q, a->gate_sc, a->up_q, a->up_sc,
+                                   a->work_hidden_q, a->work_hidden_sc, a->hidden_qt, a->hidden_sct, st));
+                return mx_down(c, d, off, limit, a->work_hidden_q, a->work_hidden_sc, a->w_routed_down_q,
+                               a->w_routed_down_sc, a->y_routed, st);
+            },
+            [&](cudaStream_t st) {
+                RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
+                comb.peers = combine_peers;
+                return launch_combine_rows(comb, move_blocks, st);
+            }));
+        MOK_TRY(pipe.join());
+        if (m > 0) MOK_TRY(pipe.fork());
     }
     return MOK_OK;
 }
@@ -426,7 +596,6 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
     if (!a) return MOK_ERR_INVALID;
     Dims d;
     MOK_TRY(check_common(a->c, d));
-    if (d.MB % 128 || d.H % 128 || d.I % 128) return MOK_ERR_INVALID;
     const mok_layer_common& c = a->c;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     PeerPtrs dy_peers{}, dxr_peers{}, rw_peers{}, drw_peers{}, x_peers{};
@@ -438,8 +607,11 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
     if (!a->router_weights_routed || !a->d_router_weight_partials) return MOK_ERR_INVALID;
     const void* dy_local = dy_peers.p[d.rank];
     const void* x_local = x_peers.p[d.rank];
-    const int move_blocks = device_sm_count() * 4;
+    const int move_blocks = move_grid();
     const int partial_cols = d.I / kBlockN;
+    Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
+    MOK_TRY(pipe.error());
+    MOK_TRY(pipe.fork());
 
     // shared expert, BF16
     MOK_TRY(run_dgrad_down(c, d, false, 0, d.T, dy_local, d.T, a->w_shared_down, a->gate_shared, a->up_shared,
@@ -463,60 +635,68 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
             MOK_TRY(mx_gate_up(c, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
                                a->w_routed_up_q, a->w_routed_up_sc, a->gate_q, a->gate_sc, a->up_q, a->up_sc,
                                a->work_hidden_q, a->work_hidden_sc, a->hidden_qt, a->hidden_sct, s));
+            MOK_TRY(pipe.fork());
         }
-        // reverse-combine: w * d_y, quantised in both layouts
-        RowMoveParams rc = row_move(c, d, off, limit, nullptr);
-        rc.peers = dy_peers;
-        rc.scale_peers = rw_peers;
-        rc.row_divisor = d.K;
-        rc.row_scale_out = a->router_weights_routed;
-        QuantOut dyo{u8(a->d_y_q), u8(a->d_y_sc), u8(a->work_d_y_qt), u8(a->work_d_y_sct), d.MB};
-        MOK_TRY(launch_dispatch_quant(rc, dyo, true, move_blocks, s));
-        {   // d_hidden = d_y @ Wd^T' (pre-transposed [El, I, H]) + SwiGLU backward
-            MxGemmParams p = mx_base(c, off, limit);
-            p.n_tiles = d.I / kBlockN;
-            p.k_tiles_per_seg = d.H / kMxBlockK;
-            p.b_rows_per_expert = d.I;
-            p.sfa0 = cu8(a->d_y_sc); p.sfa_k_tiles = d.H / 128;
-            p.sfb0 = cu8(a->w_routed_down_T_sc); p.sfb_k_tiles = d.H / 128;
-            p.out_bf16 = static_cast<__nv_bfloat16*>(a->d_hidden_routed);
-            p.ld_out = d.I;
-            p.in_q[0] = cu8(a->gate_q); p.in_sc[0] = cu8(a->gate_sc);
-            p.in_q[1] = cu8(a->up_q); p.in_sc[1] = cu8(a->up_sc);
-            p.q[0] = u8(a->d_gate_q); p.sc[0] = u8(a->d_gate_sc);
-            p.q[1] = u8(a->d_up_q); p.sc[1] = u8(a->d_up_sc);
-            p.qt[0] = u8(a->work_d_gate_qt); p.sct[0] = u8(a->work_d_gate_sct);
-            p.qt[1] = u8(a->work_d_up_qt); p.sct[1] = u8(a->work_d_up_sct);
-            p.row_scale = a->router_weights_routed;
-            p.partials = a->d_router_weight_partials;
-            MxGemmOperands o{};
-            o.a0 = a->d_y_q; o.b0 = a->w_routed_down_T_q;
-            o.a_inner = d.H; o.a_outer = d.MB;
-            o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(d.El) * d.I;
-            MOK_TRY(launch_mx_gemm(kMxEpiDgradDown, false, o, p, (limit / kBlockM) * p.n_tiles, 0, kSlotDgradDownRouted, s));
-        }
-        {   // d_x = d_gate @ Wg^T' + d_up @ Wu^T' (pre-transposed [El, H, I]) in one accumulator
-            MxGemmParams p = mx_base(c, off, limit);
-            p.n_tiles = d.H / kBlockN;
-            p.k_tiles_per_seg = d.I / kMxBlockK;
-            p.num_segs = 2;
-            p.b_rows_per_expert = d.H;
-            p.sfa0 = cu8(a->d_gate_sc); p.sfa1 = cu8(a->d_up_sc); p.sfa_k_tiles = d.I / 128;
-            p.sfb0 = cu8(a->w_routed_gate_T_sc); p.sfb1 = cu8(a->w_routed_up_T_sc); p.sfb_k_tiles = d.I / 128;
-            p.out_bf16 = static_cast<__nv_bfloat16*>(a->d_x_routed);
-            p.ld_out = d.H;
-            MxGemmOperands o{};
-            o.a0 = a->d_gate_q; o.a1 = a->d_up_q; o.b0 = a->w_routed_gate_T_q; o.b1 = a->w_routed_up_T_q;
-            o.a_inner = d.I; o.a_outer = d.MB;
-            o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(d.El) * d.H;
-            MOK_TRY(launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0, kSlotDgradGateUpRouted, s));
-        }
-        RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
-        rd.peers = dxr_peers;
-        rd.scale_peers = drw_peers;
-        rd.partials = a->d_router_weight_partials;
-        rd.partial_cols = partial_cols;
-        MOK_TRY(launch_combine_rows(rd, move_blocks, s));
+        MOK_TRY(pipe.run(m == 0,
+            [&](cudaStream_t st) {     // reverse-combine: w * d_y, quantised in both layouts
+                RowMoveParams rc = row_move(c, d, off, limit, nullptr);
+                rc.peers = dy_peers;
+                rc.scale_peers = rw_peers;
+                rc.row_divisor = d.K;
+                rc.row_scale_out = a->router_weights_routed;
+                QuantOut dyo{u8(a->d_y_q), u8(a->d_y_sc), u8(a->work_d_y_qt), u8(a->work_d_y_sct), d.MB};
+                return launch_dispatch_quant(rc, dyo, true, move_blocks, st);
+            },
+            [&](cudaStream_t st) {
+                {   // d_hidden = d_y @ Wd (weights pre-transposed to [El, I, H]) + SwiGLU backward
+                    MxGemmParams p = mx_base(c, off, limit);
+                    p.n_tiles = d.I / kBlockN;
+                    p.k_tiles_per_seg = d.H / kMxBlockK;
+                    p.b_rows_per_expert = d.I;
+                    p.sfa0 = cu8(a->d_y_sc); p.sfa_k_tiles = d.H / 128;
+                    p.sfb0 = cu8(a->w_routed_down_T_sc); p.sfb_k_tiles = d.H / 128;
+                    p.out_bf16 = static_cast<__nv_bfloat16*>(a->d_hidden_routed);
+                    p.ld_out = d.I;
+                    p.in_q[0] = cu8(a->gate_q); p.in_sc[0] = cu8(a->gate_sc);
+                    p.in_q[1] = cu8(a->up_q); p.in_sc[1] = cu8(a->up_sc);
+                    p.q[0] = u8(a->d_gate_q); p.sc[0] = u8(a->d_gate_sc);
+                    p.q[1] = u8(a->d_up_q); p.sc[1] = u8(a->d_up_sc);
+                    p.qt[0] = u8(a->work_d_gate_qt); p.sct[0] = u8(a->work_d_gate_sct);
+                    p.qt[1] = u8(a->work_d_up_qt); p.sct[1] = u8(a->work_d_up_sct);
+                    p.row_scale = a->router_weights_routed;
+                    p.partials = a->d_router_weight_partials;
+                    MxGemmOperands o{};
+                    o.a0 = a->d_y_q; o.b0 = a->w_routed_down_T_q;
+                    o.a_inner = d.H; o.a_outer = d.MB;
+                    o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(d.El) * d.I;
+                    MOK_TRY(launch_mx_gemm(kMxEpiDgradDown, false, o, p, (limit / kBlockM) * p.n_tiles, 0,
+                                           kSlotDgradDownRouted, st));
+                }
+                // d_x = d_gate @ Wg + d_up @ Wu (weights pre-transposed to [El, H, I]) in one accumulator
+                MxGemmParams p = mx_base(c, off, limit);
+                p.n_tiles = d.H / kBlockN;
+                p.k_tiles_per_seg = d.I / kMxBlockK;
+                p.num_segs = 2;
+                p.b_rows_per_expert = d.H;
+                p.sfa0 = cu8(a->d_gate_sc); p.sfa1 = cu8(a->d_up_sc); p.sfa_k_tiles = d.I / 128;
+                p.sfb0 = cu8(a->w_routed_gate_T_sc); p.sfb1 = cu8(a->w_routed_up_T_sc); p.sfb_k_tiles = d.I / 128;
+                p.out_bf16 = static_cast<__nv_bfloat16*>(a->d_x_routed);
+                p.ld_out = d.H;
+                MxGemmOperands o{};
+                o.a0 = a->d_gate_q; o.a1 = a->d_up_q; o.b0 = a->w_routed_gate_T_q; o.b1 = a->w_routed_up_T_q;
+                o.a_inner = d.I; o.a_outer = d.MB;
+                o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(d.El) * d.H;
+                return launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0, kSlotDgradGateUpRouted, st);
+            },
+            [&](cudaStream_t st) {
+                RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
+                rd.peers = dxr_peers;
+                rd.scale_peers = drw_peers;
+                rd.partials = a->d_router_weight_partials;
+                rd.partial_cols = partial_cols;
+                return launch_combine_rows(rd, move_blocks, st);
+            }));
+        MOK_TRY(pipe.join());
         const int acc = m > 0 ? 1 : 0;
         MOK_TRY(mx_wgrad(c, d, off, limit, a->work_d_y_qt, a->work_d_y_sct, d.H, a->hidden_qt, a->hidden_sct, d.I,
                          a->d_w_routed_down, acc, s));

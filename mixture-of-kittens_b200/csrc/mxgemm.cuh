@@ -44,6 +44,7 @@ struct MxGemmParams {
     int rows_host, capacity, row_offset, row_limit;
     const int* tokens_per_expert;
     int num_experts;
+    ChunkSpec chunk;               // row sub-range of the window this launch covers (not used by weight gradients)
     // tiling
     int n_tiles, m_tiles_w, k_tiles_per_seg, num_segs, b_rows_per_expert;
     // scales: [row_tiles, k_tiles, 512 B]
@@ -155,8 +156,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 
     const int n_total = p.num_tokens ? min(*p.num_tokens, p.capacity) : p.rows_host;
     const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
+    int chunk_lo = 0, chunk_hi = win_rows;
+    if (!kWgrad) chunk_range(win_rows, p.chunk, chunk_lo, chunk_hi);
+    const int m_tile0 = chunk_lo / kBlockM;
     const int num_tiles = kWgrad ? ((p.accumulate && win_rows == 0) ? 0 : E * p.m_tiles_w * p.n_tiles)
-                                 : (win_rows / kBlockM) * p.n_tiles;
+                                 : ((chunk_hi - chunk_lo) / kBlockM) * p.n_tiles;
 
     auto decode = [&](int tile, int& m_idx, int& n_idx, int& expert, int& k_row0, int& k_tiles) {
         if constexpr (kWgrad) {
@@ -171,8 +175,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             k_row0 = lo - p.row_offset;
             k_tiles = hi > lo ? (hi - lo) / kMxBlockK : 0;
         } else {
-            m_idx = tile / p.n_tiles;
-            n_idx = tile - m_idx * p.n_tiles;
+            const int m_rel = tile / p.n_tiles;
+            n_idx = tile - m_rel * p.n_tiles;
+            m_idx = m_tile0 + m_rel;
             expert = 0;
             if (p.tokens_per_expert) {
                 const int g = p.row_offset + m_idx * kBlockM;
