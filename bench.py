@@ -48,6 +48,17 @@ WORKLOADS = {
     "C3": dict(T=16384, H=4096, I=1536, E=64, K=6, router="uniform", backward=True,
                minibatch=4096, macrobatch=131072, multiplier=0.5,
                desc="BF16 fwd+bwd, 16384 tokens/rank, H=4096, 64 experts, top-6, I=1536"),
+    # MXFP8 shapes of BASELINE config 4 (EP=8: 256 experts, 32 per GPU).  "C4x1" keeps one GPU's share
+    # (32 local experts, all 16384*8 routes local) so the per-GPU work of C4 can be measured on one GPU.
+    "C4": dict(T=16384, H=7168, I=2048, E=256, K=8, router="linear", backward=True, mxfp8=True,
+               minibatch=4096, macrobatch=131072, multiplier=0.5,
+               desc="MXFP8 fwd+bwd, 16384 tokens/rank, H=7168, 256 experts, top-8, I=2048"),
+    "C4x1": dict(T=16384, H=7168, I=2048, E=32, K=8, router="linear", backward=True, mxfp8=True,
+                 minibatch=4096, macrobatch=131072, multiplier=0.5,
+                 desc="MXFP8 fwd+bwd, one GPU's share of C4: 16384 tokens, H=7168, 32 local experts, top-8, I=2048"),
+    "C4x1-bf16": dict(T=16384, H=7168, I=2048, E=32, K=8, router="linear", backward=True,
+                      minibatch=4096, macrobatch=131072, multiplier=0.5,
+                      desc="BF16 fwd+bwd at the C4x1 shapes"),
 }
 # DRAM bytes per launch of the dominant kernel from the ncu capture summarised under profiles/
 # (filled in per workload once captured; None = not captured)
@@ -164,11 +175,18 @@ def run_ours(args, rank, world, local_rank):
     dx_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
     drw_host = torch.empty(T, K, dtype=torch.float32).pin_memory()
 
+    fwd_params = bwd_params = params
+    if wl.get("mxfp8"):                  # routed weights quantised once, outside the timed region (as the reference does)
+        qg, qu, qd = (mok.ops.mxfp8_quantize(w, True, True) for w in params[3:])
+        fwd_params = params[:3] + [(qg[0], qg[1]), (qu[0], qu[1]), (qd[0], qd[1])]
+        bwd_params = params[:3] + [tuple(qg), tuple(qu), (qd[2], qd[3])]
+        params[3:] = []                  # the bf16 masters are not needed any more
+
     def step(inp):
         sched = F.build_schedule(ws, cfg, inp["topk"], num_local_experts=El)
-        out, ctx = F.forward(cfg, ws, sched, inp["x"], inp["rw"], *params)
+        out, ctx = F.forward(cfg, ws, sched, inp["x"], inp["rw"], *fwd_params)
         if wl["backward"]:
-            grads = F.backward(cfg, ws, sched, ctx, inp["d_out"], inp["x"], inp["rw"], *params)
+            grads = F.backward(cfg, ws, sched, ctx, inp["d_out"], inp["x"], inp["rw"], *bwd_params)
             return out, grads
         return out, None
 
@@ -222,6 +240,8 @@ def run_ours(args, rank, world, local_rank):
 
     flops = layer_flops(T, K, H, I, wl["backward"])
     peaks = measured_peaks()
+    if wl.get("mxfp8"):                  # no measured MXFP8 peak on file: twice the measured bf16 figures
+        peaks = dict(peaks, tflops=2 * peaks["tflops"], burst=2 * peaks["burst"], source=peaks["source"] + " x2 for fp8")
     dom = "gemm_gate_up_swiglu_routed"
     dom_ms, dom_cnt = prof.get(dom, (0.0, 0))
     dom_ms_step = dom_ms / args.steps if dom_cnt else None
@@ -234,7 +254,8 @@ def run_ours(args, rank, world, local_rank):
     line = {
         "metric": METRIC, "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": UNIT,
         "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "mxfp8 (e4m3 x e8m0, fp32 accumulate)" if wl.get("mxfp8") else "bf16", "data": "synthetic",
         "config": {"workload": f"{name}: {wl['desc']}", "ep_size": world, "tokens_per_rank": T, "hidden": H,
                    "intermediate": I, "experts": E, "topk": K, "minibatch_size": wl["minibatch"],
                    "macrobatch_size": wl["macrobatch"], "pass": "fwd+bwd" if wl["backward"] else "fwd (incl. build_schedule)",
@@ -305,7 +326,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="auto", choices=["auto", "C2", "C3"])
+    ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per rank (profiling a reduced case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()

@@ -303,7 +303,7 @@ int move_grid() {
 int pipeline_chunks(const mok_layer_common& c, int limit) {
     static const int configured = [] {
         const char* e = std::getenv("MOK_B200_CHUNKS");
-        const int v = e ? std::atoi(e) : 8;
+        const int v = e ? std::atoi(e) : 1;
         return v < 1 ? 1 : (v > 32 ? 32 : v);
     }();
     const int by_minibatch = limit / c.minibatch_size;
@@ -693,7 +693,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                 rd.peers = dxr_peers;
                 rd.scale_peers = drw_peers;
                 rd.partials = a->d_router_weight_partials;
-                rd.partial_cols = partial_cols;
+                rd.partial_cols = 2 * partial_cols   /* the MXFP8 epilogue writes one partial per 128-column half */;
                 return launch_combine_rows(rd, move_blocks, st);
             }));
         MOK_TRY(pipe.join());

@@ -14,7 +14,7 @@ int launch_mx_inst(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorM
         MOK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMxSmemBytes));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kern<<<grid, kGemmThreads, kMxSmemBytes, stream>>>(a0, b0, a1, b1, p);
+    kern<<<grid, kMxThreads, kMxSmemBytes, stream>>>(a0, b0, a1, b1, p);
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
 }

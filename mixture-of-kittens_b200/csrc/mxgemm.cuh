@@ -35,7 +35,9 @@ constexpr int kMxABytes = kBlockM * kMxBlockK;        // 16 KB
 constexpr int kMxBBytes = kBlockN * kMxBlockK;        // 32 KB
 constexpr int kMxTileBytes = kMxABytes + kMxBBytes;
 constexpr int kMxSfBytes = 512 + 1024;                // A scales + B scales per stage
-constexpr int kMxSmemBytes = kStages * (kMxTileBytes + kMxSfBytes) + 256 + kMaxExperts * 4 + 1024;
+constexpr int kMxThreads = 64 + 256;                  // producer warp, MMA warp, eight epilogue warps
+constexpr int kMxTrBytes = 8 * 32 * 17 * 4;           // per-epilogue-warp transpose tiles
+constexpr int kMxSmemBytes = kStages * (kMxTileBytes + kMxSfBytes) + 256 + kMaxExperts * 4 + kMxTrBytes + 1024;
 constexpr int kMxAccCols = 256, kMxSfaCol = 256, kMxSfbCol = 260;
 
 struct MxGemmParams {
@@ -91,26 +93,34 @@ __device__ __forceinline__ void mx_store_normal(const uint32_t (&w)[16], uint8_t
     dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
     sc[mx_scale_offset(static_cast<int>(row), col0 >> 5, cols >> 7)] = static_cast<uint8_t>(sb);
 }
-// quantise the same chunk along the token axis: the warp's 32 lanes hold rows row0..row0+31 (one MX
-// block) of 32 columns; column j's block is reduced with redux.sync and written to qt[col0+j][row]
-__device__ __forceinline__ void mx_store_transposed(const uint32_t (&w)[16], uint8_t* qt, uint8_t* sct, size_t row, int col0,
-                                                    int t_rows, int lane) {
-    uint32_t my_scale = 0;
+// quantise the same chunk along the token axis.  The warp's 32 lanes hold rows row0..row0+31 (one MX
+// block) of 32 columns; the chunk is transposed through a padded per-warp shared-memory tile so that
+// lane j ends up with column j's 32 values and writes its 32 bytes to qt[col0+j][row0..row0+31].
+constexpr int kMxTrWords = 32 * 17;
+__device__ __forceinline__ void mx_store_transposed(const uint32_t (&w)[16], uint32_t* tr, uint8_t* qt, uint8_t* sct, size_t row,
+                                                    int col0, int t_rows, int lane) {
+    __syncwarp();
 #pragma unroll
-    for (int j = 0; j < 32; ++j) {
-        const uint32_t word = w[j >> 1];
-        const uint32_t bits = ((j & 1) ? (word & 0xFFFF0000u) : (word << 16));      // bf16 -> fp32 bit pattern
-        const uint32_t amax_bits = __reduce_max_sync(0xffffffffu, bits & 0x7FFFFFFFu);
-        const uint32_t sb = mx_scale_byte(__uint_as_float(amax_bits));
-        const float v = __uint_as_float(bits) * mx_inv_scale(sb);
-        qt[static_cast<size_t>(col0 + j) * t_rows + row] = static_cast<uint8_t>(mx_pack2(v, 0.0f) & 0xFFu);
-        if (lane == j) my_scale = sb;
+    for (int i = 0; i < 16; ++i) tr[lane * 17 + i] = w[i];
+    __syncwarp();
+    uint32_t in[16], out[8], sb;
+    const int wsel = lane >> 1, hsel = (lane & 1) * 16;
+#pragma unroll
+    for (int r2 = 0; r2 < 16; ++r2) {
+        const uint32_t lo = (tr[(2 * r2) * 17 + wsel] >> hsel) & 0xFFFFu;
+        const uint32_t hi = (tr[(2 * r2 + 1) * 17 + wsel] >> hsel) & 0xFFFFu;
+        in[r2] = lo | (hi << 16);
     }
-    sct[mx_scale_offset(col0 + lane, static_cast<int>(row >> 5), t_rows >> 7)] = static_cast<uint8_t>(my_scale);
+    mx_quantize_block(in, out, sb);
+    const size_t row0 = row - lane;
+    uint4* dst = reinterpret_cast<uint4*>(qt + static_cast<size_t>(col0 + lane) * t_rows + row0);
+    dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
+    dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+    sct[mx_scale_offset(col0 + lane, static_cast<int>(row0 >> 5), t_rows >> 7)] = static_cast<uint8_t>(sb);
 }
 
 template <int kEpi, bool kWgrad>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kMxThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                const MxGemmParams p) {
@@ -124,6 +134,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     int* s_end = reinterpret_cast<int*>(sf_smem + kStages * kMxSfBytes + 256);
+    uint32_t* tr_smem = reinterpret_cast<uint32_t*>(sf_smem + kStages * kMxSfBytes + 256 + kMaxExperts * 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int E = p.tokens_per_expert ? p.num_experts : 1;
@@ -133,7 +144,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(tfull_bar, 1);
-        mbar_init(tempty_bar, 4);
+        mbar_init(tempty_bar, 8);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -272,8 +283,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
+        // Eight warps: two per TMEM lane quarter (a warp may only read lanes 32*(warp%4)...), each
+        // taking half of the tile's columns, so a thread holds 128 accumulator columns as 64 packed words.
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r_in_tile = quarter * 32 + lane;
+        uint32_t* tr = tr_smem + (warp - 2) * kMxTrWords;
         int it = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
@@ -282,11 +297,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             if (!mbar_wait(tfull_bar, it & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-            uint32_t pk[128];     // the thread's accumulator row as packed bf16 pairs
+            uint32_t pk[64];
 #pragma unroll
-            for (int c = 0; c < kBlockN / 32; ++c) {
+            for (int c = 0; c < 4; ++c) {
+                // GateUp: chunks {2h, 2h+1} of the gate half and the same two of the up half; else 4 consecutive chunks
+                const int col = (kEpi == kMxEpiGateUp) ? ((c >> 1) * (kBlockN / 2) + (half * 2 + (c & 1)) * 32) : (half * 4 + c) * 32;
                 uint32_t acc[32];
-                if (k_tiles > 0) { tmem_ld_32x32(t_addr + c * 32, acc); tmem_ld_wait(); }
+                if (k_tiles > 0) { tmem_ld_32x32(t_addr + col, acc); tmem_ld_wait(); }
                 else {
 #pragma unroll
                     for (int i = 0; i < 32; ++i) acc[i] = 0u;
@@ -302,10 +319,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             if constexpr (kEpi == kMxEpiStore) {
                 if (!(kWgrad && p.accumulate && k_tiles == 0)) {
                     __nv_bfloat16* dst = p.out_bf16 + (kWgrad ? static_cast<size_t>(expert) * p.out_expert_stride : 0) +
-                                         row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN;
+                                         row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN + half * 128;
                     uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-                    for (int v = 0; v < 32; ++v) {
+                    for (int v = 0; v < 16; ++v) {
                         uint32_t o[4] = {pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]};
                         if (kWgrad && p.accumulate) {
                             const uint4 old = d4[v];
@@ -321,13 +338,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 }
             } else if constexpr (kEpi == kMxEpiGateUp) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    const int col0 = n_idx * (kBlockN / 2) + c * 32;
+                for (int c = 0; c < 2; ++c) {
+                    const int col0 = n_idx * (kBlockN / 2) + (half * 2 + c) * 32;
                     uint32_t g[16], u[16], h[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         g[i] = pk[c * 16 + i];
-                        u[i] = pk[64 + c * 16 + i];
+                        u[i] = pk[32 + c * 16 + i];
                         float2 gf = unpack_bf16(g[i]), uf = unpack_bf16(u[i]);
                         if (p.has_limit) {
                             gf.x = fminf(gf.x, p.limit); gf.y = fminf(gf.y, p.limit);
@@ -338,21 +355,26 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     mx_store_normal(g, p.q[0], p.sc[0], row, col0, p.q_cols);
                     mx_store_normal(u, p.q[1], p.sc[1], row, col0, p.q_cols);
                     mx_store_normal(h, p.q[2], p.sc[2], row, col0, p.q_cols);
-                    mx_store_transposed(h, p.qt[2], p.sct[2], row, col0, p.t_rows, lane);
+                    mx_store_transposed(h, tr, p.qt[2], p.sct[2], row, col0, p.t_rows, lane);
                 }
             } else {
                 float inv_w = 0.0f;
                 if (p.row_scale) { const float w = p.row_scale[row]; inv_w = w > 0.0f ? 1.0f / w : 0.0f; }
                 float partial = 0.0f;
-                uint4* dh4 = reinterpret_cast<uint4*>(p.out_bf16 + row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN);
+                const int colbase = n_idx * kBlockN + half * 128;
+                uint4* dh4 = reinterpret_cast<uint4*>(p.out_bf16 + row * p.ld_out + colbase);
+                const size_t so0 = mx_scale_offset(static_cast<int>(row), colbase >> 5, p.q_cols >> 7);   // 4 consecutive bytes
+                const uint32_t gsc4 = *reinterpret_cast<const uint32_t*>(p.in_sc[0] + so0);
+                const uint32_t usc4 = *reinterpret_cast<const uint32_t*>(p.in_sc[1] + so0);
+                const uint4* gq = reinterpret_cast<const uint4*>(p.in_q[0] + row * p.q_cols + colbase);
+                const uint4* uq = reinterpret_cast<const uint4*>(p.in_q[1] + row * p.q_cols + colbase);
+                uint4 gnext0 = gq[0], gnext1 = gq[1], unext0 = uq[0], unext1 = uq[1];
 #pragma unroll
-                for (int c = 0; c < 8; ++c) {
-                    const int col0 = n_idx * kBlockN + c * 32;
-                    const uint4* gq = reinterpret_cast<const uint4*>(p.in_q[0] + row * p.q_cols + col0);
-                    const uint4* uq = reinterpret_cast<const uint4*>(p.in_q[1] + row * p.q_cols + col0);
-                    const uint4 g0 = gq[0], g1 = gq[1], u0 = uq[0], u1 = uq[1];
-                    const size_t so = mx_scale_offset(static_cast<int>(row), col0 >> 5, p.q_cols >> 7);
-                    const float gs = mx_scale_value(p.in_sc[0][so]), us = mx_scale_value(p.in_sc[1][so]);
+                for (int c = 0; c < 4; ++c) {
+                    const int col0 = colbase + c * 32;
+                    const uint4 g0 = gnext0, g1 = gnext1, u0 = unext0, u1 = unext1;
+                    if (c + 1 < 4) { gnext0 = gq[2 * c + 2]; gnext1 = gq[2 * c + 3]; unext0 = uq[2 * c + 2]; unext1 = uq[2 * c + 3]; }
+                    const float gs = mx_scale_value((gsc4 >> (8 * c)) & 0xFFu), us = mx_scale_value((usc4 >> (8 * c)) & 0xFFu);
                     const uint32_t gb[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
                     const uint32_t ub[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
                     uint32_t dg[16], du[16];
@@ -381,10 +403,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                         dh4[c * 4 + v] = make_uint4(pk[c * 16 + 4 * v], pk[c * 16 + 4 * v + 1], pk[c * 16 + 4 * v + 2], pk[c * 16 + 4 * v + 3]);
                     mx_store_normal(dg, p.q[0], p.sc[0], row, col0, p.q_cols);
                     mx_store_normal(du, p.q[1], p.sc[1], row, col0, p.q_cols);
-                    mx_store_transposed(dg, p.qt[0], p.sct[0], row, col0, p.t_rows, lane);
-                    mx_store_transposed(du, p.qt[1], p.sct[1], row, col0, p.t_rows, lane);
+                    mx_store_transposed(dg, tr, p.qt[0], p.sct[0], row, col0, p.t_rows, lane);
+                    mx_store_transposed(du, tr, p.qt[1], p.sct[1], row, col0, p.t_rows, lane);
                 }
-                if (p.partials) p.partials[row * p.n_tiles + n_idx] = partial;
+                if (p.partials) p.partials[row * (2 * p.n_tiles) + 2 * n_idx + half] = partial;   // two column halves per tile
             }
         }
     }
