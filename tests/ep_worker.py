@@ -35,16 +35,20 @@ def main():
     torch.cuda.set_device(dev)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     F = mok.functional
-    cases = [dict(T=512, H=256, I=256, E=2 * world, K=2, limit=None, macro=131072, zipf=None),
-             dict(T=1024, H=512, I=512, E=4 * world, K=4, limit=1.0, macro=131072, zipf=None),
-             dict(T=512, H=256, I=256, E=2 * world, K=2, limit=None, macro=512, zipf=1.2)]
+    cases = [dict(T=512, H=256, I=256, E=2 * world, K=2, limit=None, macro=131072, zipf=None, mx=False),
+             dict(T=1024, H=512, I=512, E=4 * world, K=4, limit=1.0, macro=131072, zipf=None, mx=False),
+             dict(T=512, H=256, I=256, E=2 * world, K=2, limit=None, macro=512, zipf=1.2, mx=False),
+             dict(T=512, H=256, I=512, E=2 * world, K=2, limit=None, macro=131072, zipf=None, mx=True),
+             dict(T=512, H=512, I=256, E=2 * world, K=3, limit=None, macro=512, zipf=1.2, mx=True)]
     worst, failures = 0.0, []
     for ci, c in enumerate(cases):
         shape = dict(T=c["T"], H=c["H"], I=c["I"], E=c["E"], W=world, K=c["K"], seed=40 + ci, zipf_s=c["zipf"])
         ranks = [O.make_rank_inputs(r, **shape) for r in range(world)]
         mult = 1.0                                # capacity = T*K*max(2, W): nothing can overflow
         cap = c["T"] * c["K"] * max(2, world)
-        ref = O.layer_forward_backward(ranks, swiglu_limit=c["limit"], device_rounding=True, capacity=cap)[rank]
+        ref = O.layer_forward_backward(ranks, swiglu_limit=c["limit"], device_rounding=True, capacity=cap,
+                                       mxfp8=c["mx"])[rank]
+        tol = 3e-2 if c["mx"] else 1e-2
         cfg = F.MoKConfig(minibatch_size=256, macrobatch_size=c["macro"], schedule_capacity_multiplier=mult,
                           all_gather_top_experts_chunk_bytes=16)
         ws = F.get_workspace(cfg, dist.group.WORLD, device=dev, num_local_tokens=c["T"], hidden_size=c["H"], topk=c["K"])
@@ -53,11 +57,16 @@ def main():
         w = [d(t) for t in (me.w_shared_gate, me.w_shared_up, me.w_shared_down, me.w_routed_gate, me.w_routed_up,
                             me.w_routed_down)]
         x, rw = d(me.x), d(me.router_weights)
+        fw = bw = w
+        if c["mx"]:
+            qg, qu, qd = (mok.ops.mxfp8_quantize(t, True, True) for t in w[3:])
+            fw = w[:3] + [(qg[0], qg[1]), (qu[0], qu[1]), (qd[0], qd[1])]
+            bw = w[:3] + [tuple(qg), tuple(qu), (qd[2], qd[3])]
         outs = []
         for rep in range(2):                      # second pass: bit-identical
             sched = F.build_schedule(ws, cfg, d(me.topk_experts), num_local_experts=c["E"] // world)
-            out, ctx = F.forward(cfg, ws, sched, x, rw, *w, swiglu_limit=c["limit"])
-            grads = F.backward(cfg, ws, sched, ctx, d(me.d_output), x, rw, *w, swiglu_limit=c["limit"])
+            out, ctx = F.forward(cfg, ws, sched, x, rw, *fw, swiglu_limit=c["limit"])
+            grads = F.backward(cfg, ws, sched, ctx, d(me.d_output), x, rw, *bw, swiglu_limit=c["limit"])
             torch.cuda.synchronize()
             outs.append((out, grads))
         code = mok.last_status(dev)[0]
@@ -70,12 +79,12 @@ def main():
                 failures.append(f"case {ci}: schedule table {name} differs")
         e = rel(ref["output"].float(), outs[1][0].float())
         worst = max(worst, e)
-        if e > 1e-2:
+        if e > tol:
             failures.append(f"case {ci}: output rel-L2 {e:.3e}")
         for name, g_ in zip(GRADS, outs[1][1]):
             e = rel(ref[name].float(), g_.float())
             worst = max(worst, e)
-            if e > 1e-2:
+            if e > tol:
                 failures.append(f"case {ci}: {name} rel-L2 {e:.3e}")
         if not torch.equal(outs[0][0], outs[1][0]) or any(not torch.equal(a, b) for a, b in zip(outs[0][1], outs[1][1])):
             failures.append(f"case {ci}: two runs differ bitwise")
