@@ -101,149 +101,216 @@ __global__ void __launch_bounds__(256) epilogue_kernel(const uint4* __restrict__
 }  // namespace
 
 // ---------------------------------------------------------------------------------------
-// dispatch: local row i <- peer[peer_rank[i]] row (peer_token_idx[i] / row_divisor); padding rows
-// (peer_rank < 0) become zeros.  Optionally scales the row by a per-row float and re-rounds to bf16
-// (backward "reverse combine").  One warp per row, 16-byte vectors, several loads in flight.
-// ---------------------------------------------------------------------------------------
-template <bool kScale>
-__global__ void __launch_bounds__(256) dispatch_rows_kernel(RowMoveParams p) {
-    const int n_total = min(*p.num_tokens, p.capacity);
-    const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
-    int row_lo, rows;
-    chunk_range(win_rows, p.chunk, row_lo, rows);
-    const int warps_per_block = blockDim.x >> 5;
-    const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    const int n_warps = gridDim.x * warps_per_block;
-    const int vec_per_row = p.hidden >> 3;
-    for (int row = row_lo + warp; row < rows; row += n_warps) {
-        const int g = p.row_offset + row;
-        const int pr = p.peer_rank[g];
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.local) + static_cast<size_t>(row) * p.hidden);
-        if (pr < 0) {
-            for (int v = lane; v < vec_per_row; v += 32) dst[v] = make_uint4(0, 0, 0, 0);
-            if (kScale && lane == 0) p.row_scale_out[row] = 0.0f;
-            continue;
-        }
-        const int tok = p.peer_token_idx[g];
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.peers.p[pr]) +
-                                                           static_cast<size_t>(tok / p.row_divisor) * p.hidden);
-        float w = 1.0f;
-        if (kScale) {
-            w = static_cast<const float*>(p.scale_peers.p[pr])[tok];
-            if (lane == 0) p.row_scale_out[row] = w;
-        }
-        for (int v0 = lane; v0 < vec_per_row; v0 += 128) {
-            uint4 buf[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (v0 + j * 32 < vec_per_row) buf[j] = src[v0 + j * 32];
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (v0 + j * 32 < vec_per_row) {
-                    uint4 o = buf[j];
-                    if (kScale) {
-                        uint32_t* w32 = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            const float2 f = unpack_bf16(w32[q]);
-                            w32[q] = pack_bf16(f.x * w, f.y * w);
-                        }
-                    }
-                    dst[v0 + j * 32] = o;
-                }
-            }
-        }
-    }
+// Row movement with the bulk-copy engine.  dispatch: local row i <- peer[peer_rank[i]] row
+// (peer_token_idx[i] / row_divisor), padding rows (peer_rank < 0) become zeros, optionally scaled by
+// the route's router weight and re-rounded to bf16 (backward "reverse combine").  combine:
+// peer[peer_rank[i]] row peer_token_idx[i] <- local row i (padding rows skipped); with `partials` set it
+// also sums the row's router-gradient partials in column order and stores the float at the peer.
+//
+// A row is cut into pieces of at most 4 KB.  Each warp owns two 4 KB shared-memory slots and runs a
+// two-deep pipeline: cp.async.bulk global(peer) -> shared, completion on an mbarrier, then
+// cp.async.bulk shared -> global(peer).  Only one lane issues the copies, so the kernel puts almost no
+// load on the SM's load/store path and can share SMs with the GEMM CTAs; bytes in flight per SM are
+// set by the slots (24 KB per CTA), not by registers.  Remote addresses are plain unicast peer
+// mappings; no multicast.
+enum : int { kMoveDispatch = 0, kMoveDispatchScale = 1, kMoveCombine = 2 };
+constexpr int kMoveWarps = 3;
+constexpr int kMovePiece = 4096;
+
+__device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes)
+                 : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
-// combine: peer[peer_rank[i]] row peer_token_idx[i] <- local row i (padding rows skipped).  With
-// `partials` set it also sums the router-gradient partials of the row in column order and stores
-// the float at peer[...]'s d_router_weight[peer_token_idx[i]].
-__global__ void __launch_bounds__(256) combine_rows_kernel(RowMoveParams p) {
+template <int kMode>
+__global__ void __launch_bounds__(kMoveWarps * 32) move_rows_kernel(RowMoveParams p) {
+    __shared__ __align__(128) uint8_t slots[kMoveWarps][2][kMovePiece];
+    __shared__ __align__(8) uint64_t bars[kMoveWarps][2];
+    __shared__ int abort_word;
+    volatile int* abort_flag = &abort_word;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        abort_word = 0;
+        for (int w = 0; w < kMoveWarps; ++w) { mbar_init(&bars[w][0], 1); mbar_init(&bars[w][1], 1); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
     const int n_total = min(*p.num_tokens, p.capacity);
     const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
-    int row_lo, rows;
-    chunk_range(win_rows, p.chunk, row_lo, rows);
-    const int warps_per_block = blockDim.x >> 5;
-    const int warp = blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-    const int lane = threadIdx.x & 31;
-    const int n_warps = gridDim.x * warps_per_block;
-    const int vec_per_row = p.hidden >> 3;
-    for (int row = row_lo + warp; row < rows; row += n_warps) {
+    int row_lo, row_hi;
+    chunk_range(win_rows, p.chunk, row_lo, row_hi);
+    const int row_bytes = p.hidden * 2;
+    const int pieces = (row_bytes + kMovePiece - 1) / kMovePiece;
+    const long long units = static_cast<long long>(row_hi - row_lo) * pieces;
+    const long long gwarp = static_cast<long long>(blockIdx.x) * kMoveWarps + warp;
+    const long long nwarps = static_cast<long long>(gridDim.x) * kMoveWarps;
+
+    // resolve unit -> (source, destination, bytes); returns false for rows that move nothing
+    auto resolve = [&](long long unit, const uint8_t*& src, uint8_t*& dst, uint32_t& bytes, float& w, int& row, int& piece) {
+        row = row_lo + static_cast<int>(unit / pieces);
+        piece = static_cast<int>(unit % pieces);
         const int g = p.row_offset + row;
         const int pr = p.peer_rank[g];
-        if (pr < 0) continue;
+        const int off = piece * kMovePiece;
+        bytes = static_cast<uint32_t>(min(kMovePiece, row_bytes - off));
+        w = 0.0f;
+        uint8_t* local = static_cast<uint8_t*>(p.local) + static_cast<size_t>(row) * row_bytes + off;
+        if (pr < 0) { src = nullptr; dst = local; return false; }
         const int tok = p.peer_token_idx[g];
-        const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.local) + static_cast<size_t>(row) * p.hidden);
-        uint4* dst = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.peers.p[pr]) + static_cast<size_t>(tok) * p.hidden);
-        for (int v0 = lane; v0 < vec_per_row; v0 += 128) {
-            uint4 buf[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (v0 + j * 32 < vec_per_row) buf[j] = src[v0 + j * 32];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                if (v0 + j * 32 < vec_per_row) dst[v0 + j * 32] = buf[j];
+        if (kMode == kMoveCombine) {
+            src = local;
+            dst = static_cast<uint8_t*>(p.peers.p[pr]) + static_cast<size_t>(tok) * row_bytes + off;
+        } else {
+            src = static_cast<const uint8_t*>(p.peers.p[pr]) + static_cast<size_t>(tok / p.row_divisor) * row_bytes + off;
+            dst = local;
+            if (kMode == kMoveDispatchScale) w = static_cast<const float*>(p.scale_peers.p[pr])[tok];
         }
-        if (p.partials != nullptr && lane == 0) {
+        return true;
+    };
+
+    uint32_t phase[2] = {0, 0};
+    long long issued = 0;        // copies this warp has put in flight (slot = issued & 1)
+    bool ok = true;
+    // software pipeline: the load of unit u+1 is in flight while unit u is stored
+    const uint8_t* src_n = nullptr; uint8_t* dst_n = nullptr; uint32_t bytes_n = 0; float w_n = 0.f; int row_n = 0, piece_n = 0;
+    bool live_n = false, have_n = false;
+    long long u = gwarp;
+    auto start_load = [&](long long unit) {
+        have_n = unit < units;
+        if (!have_n) return;
+        live_n = resolve(unit, src_n, dst_n, bytes_n, w_n, row_n, piece_n);
+        if (live_n && lane == 0) {
+            const int slot = static_cast<int>(issued & 1);
+            // the slot was last read by the store committed in the previous iteration
+            if (issued >= 2) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+            mbar_arrive_expect_tx(&bars[warp][slot], bytes_n);
+            bulk_g2s(slots[warp][slot], src_n, bytes_n, &bars[warp][slot]);
+        }
+        if (live_n) ++issued;
+    };
+    start_load(u);
+    while (have_n && ok) {
+        const uint8_t* src = src_n; uint8_t* dst = dst_n; const uint32_t bytes = bytes_n; const float w = w_n;
+        const int row = row_n, piece = piece_n; const bool live = live_n;
+        const int slot = static_cast<int>((issued - 1) & 1);
+        (void)src;
+        u += nwarps;
+        start_load(u);                                  // may bump `issued`; `slot` above was taken before
+        if (!live) {
+            if (kMode != kMoveCombine) {                // padding row of a dispatch: zeros
+                uint4* d4 = reinterpret_cast<uint4*>(dst);
+                for (uint32_t v = lane; v < bytes / 16; v += 32) d4[v] = make_uint4(0, 0, 0, 0);
+                if (kMode == kMoveDispatchScale && piece == 0 && lane == 0) p.row_scale_out[row] = 0.0f;
+            }
+            continue;
+        }
+        if (!mbar_wait(&bars[warp][slot], phase[slot], abort_flag)) { ok = false; break; }
+        phase[slot] ^= 1;
+        if (kMode == kMoveDispatchScale) {
+            uint4* s4 = reinterpret_cast<uint4*>(slots[warp][slot]);
+            for (uint32_t v = lane; v < bytes / 16; v += 32) {
+                uint4 q = s4[v];
+                uint32_t* w32 = reinterpret_cast<uint32_t*>(&q);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) { const float2 f = unpack_bf16(w32[k]); w32[k] = pack_bf16(f.x * w, f.y * w); }
+                s4[v] = q;
+            }
+            if (piece == 0 && lane == 0) p.row_scale_out[row] = w;
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+        }
+        if (lane == 0) bulk_s2g(dst, slots[warp][slot], bytes);
+        if (kMode == kMoveCombine && p.partials != nullptr && piece == 0 && lane == 0) {
             float s = 0.0f;
             for (int c = 0; c < p.partial_cols; ++c) s += p.partials[static_cast<size_t>(row) * p.partial_cols + c];
-            static_cast<float*>(p.scale_peers.p[pr])[tok] = s;
+            const int g = p.row_offset + row;
+            static_cast<float*>(p.scale_peers.p[p.peer_rank[g]])[p.peer_token_idx[g]] = s;
         }
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    __syncwarp();
+    if (!ok && lane == 0) report_status(p.status, MOK_STATUS_PIPELINE_TIMEOUT, 200 + kMode);
 }
 
 // dispatch + MXFP8 quantisation.  Work unit = 32 consecutive rows (one MX block along the token axis)
-// x 256 columns, staged in shared memory: coalesced row gathers in, then one normal block and one
-// transposed block per thread out.  Padding rows are zeros (scale byte 88, as the reference's
-// device code produces for an all-zero block).
+// x 256 columns.  Warp 0 fetches the 32 row pieces (512 B each, from whichever peer owns the row) with
+// cp.async.bulk into one of two shared-memory tiles while all eight warps quantise the other tile: one
+// 1x32 block along the row and one 32x1 block along the tokens per thread.  Padding rows are zeros
+// (scale byte 88, as the reference's device code produces for an all-zero block).  kScale multiplies
+// every row by its route's router weight and re-rounds to bf16 first (backward "reverse combine").
 template <bool kScale>
 __global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, QuantOut o) {
-    constexpr int kCols = 256, kStride = kCols + 8;
-    __shared__ __align__(16) __nv_bfloat16 tile[32 * kStride];
+    constexpr int kCols = 256, kRowBytes = kCols * 2;
+    __shared__ __align__(128) uint8_t tiles[2][32 * kRowBytes];
+    __shared__ float s_w[2][32];
+    __shared__ __align__(8) uint64_t bars[2];
+    __shared__ int abort_word;
+    volatile int* abort_flag = &abort_word;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) { abort_word = 0; mbar_init(&bars[0], 1); mbar_init(&bars[1], 1); mbar_fence_init(); }
+    __syncthreads();
+
     const int n_total = min(*p.num_tokens, p.capacity);
     const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
     int row_lo, row_hi;
     chunk_range(win_rows, p.chunk, row_lo, row_hi);
     const int col_chunks = p.hidden / kCols;
     const int units = ((row_hi - row_lo) / 32) * col_chunks;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+
+    auto fetch = [&](int unit, int buf) {           // warp 0 only
+        const int rb = unit / col_chunks, cc = unit - rb * col_chunks;
+        const int row = row_lo + rb * 32 + lane, col0 = cc * kCols;
+        const int g = p.row_offset + row;
+        const int pr = p.peer_rank[g];
+        const uint8_t* src = nullptr;
+        float w = 0.0f;
+        if (pr >= 0) {
+            const int tok = p.peer_token_idx[g];
+            src = static_cast<const uint8_t*>(p.peers.p[pr]) + (static_cast<size_t>(tok / p.row_divisor) * p.hidden + col0) * 2;
+            w = kScale ? static_cast<const float*>(p.scale_peers.p[pr])[tok] : 1.0f;
+        } else {
+            uint4* z = reinterpret_cast<uint4*>(&tiles[buf][lane * kRowBytes]);
+#pragma unroll
+            for (int v = 0; v < kRowBytes / 16; ++v) z[v] = make_uint4(0, 0, 0, 0);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // later bulk copies reuse this row
+        }
+        s_w[buf][lane] = w;
+        if (kScale && cc == 0) p.row_scale_out[row] = w;
+        const unsigned live = __ballot_sync(0xffffffffu, pr >= 0);
+        __syncwarp();
+        if (lane == 0) mbar_arrive_expect_tx(&bars[buf], __popc(live) * kRowBytes);
+        __syncwarp();
+        if (pr >= 0) bulk_g2s(&tiles[buf][lane * kRowBytes], src, kRowBytes, &bars[buf]);
+    };
+
+    uint32_t phase[2] = {0, 0};
+    int buf = 0;
+    if (warp == 0 && blockIdx.x < units) fetch(blockIdx.x, 0);
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x, buf ^= 1) {
+        const int next = unit + gridDim.x;
+        if (warp == 0 && next < units) fetch(next, buf ^ 1);      // the other tile was released by the barrier below
+        if (!mbar_wait(&bars[buf], phase[buf], abort_flag)) break;
+        phase[buf] ^= 1;
         const int rb = unit / col_chunks, cc = unit - rb * col_chunks;
         const int row0 = row_lo + rb * 32, col0 = cc * kCols;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int r = warp * 4 + i;
-            const int g = p.row_offset + row0 + r;
-            const int pr = p.peer_rank[g];
-            uint4 v = make_uint4(0, 0, 0, 0);
-            float w = 0.0f;
-            if (pr >= 0) {
-                const int tok = p.peer_token_idx[g];
-                const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.peers.p[pr]) +
-                                                                   static_cast<size_t>(tok / p.row_divisor) * p.hidden + col0);
-                v = src[lane];
-                if (kScale) {
-                    w = static_cast<const float*>(p.scale_peers.p[pr])[tok];
-                    uint32_t* w32 = reinterpret_cast<uint32_t*>(&v);
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const float2 f = unpack_bf16(w32[q]);
-                        w32[q] = pack_bf16(f.x * w, f.y * w);
-                    }
-                }
-            }
-            if (kScale && cc == 0 && lane == 0) p.row_scale_out[row0 + r] = w;
-            *reinterpret_cast<uint4*>(&tile[r * kStride + lane * 8]) = v;
-        }
-        __syncthreads();
+        const __nv_bfloat16* tile = reinterpret_cast<const __nv_bfloat16*>(tiles[buf]);
         {   // normal: thread -> (row, 32-wide block)
             const int r = threadIdx.x >> 3, kb = threadIdx.x & 7;
             uint32_t in[16], out[8], sb;
-            const uint4* src = reinterpret_cast<const uint4*>(&tile[r * kStride + kb * 32]);
+            const uint4* src = reinterpret_cast<const uint4*>(&tile[r * kCols + kb * 32]);
+            const float w = s_w[buf][r];
 #pragma unroll
             for (int j = 0; j < 4; ++j) { const uint4 v = src[j]; in[4 * j] = v.x; in[4 * j + 1] = v.y; in[4 * j + 2] = v.z; in[4 * j + 3] = v.w; }
+            if (kScale) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) { const float2 f = unpack_bf16(in[j]); in[j] = pack_bf16(f.x * w, f.y * w); }
+            }
             mx_quantize_block(in, out, sb);
             uint4* dst = reinterpret_cast<uint4*>(o.q + static_cast<size_t>(row0 + r) * p.hidden + col0 + kb * 32);
             dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
@@ -255,9 +322,9 @@ __global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, Qu
             uint32_t in[16], out[8], sb;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
-                const uint16_t lo = *reinterpret_cast<const uint16_t*>(&tile[(2 * j) * kStride + c]);
-                const uint16_t hi = *reinterpret_cast<const uint16_t*>(&tile[(2 * j + 1) * kStride + c]);
-                in[j] = static_cast<uint32_t>(lo) | (static_cast<uint32_t>(hi) << 16);
+                float lo = __bfloat162float(tile[(2 * j) * kCols + c]), hi = __bfloat162float(tile[(2 * j + 1) * kCols + c]);
+                if (kScale) { lo *= s_w[buf][2 * j]; hi *= s_w[buf][2 * j + 1]; }
+                in[j] = pack_bf16(lo, hi);
             }
             mx_quantize_block(in, out, sb);
             uint4* dst = reinterpret_cast<uint4*>(o.qt + static_cast<size_t>(col0 + c) * o.t_rows + row0);
@@ -265,8 +332,9 @@ __global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, Qu
             dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
             o.sct[mx_scale_offset(col0 + c, row0 >> 5, o.t_rows >> 7)] = static_cast<uint8_t>(sb);
         }
-        __syncthreads();
+        __syncthreads();                              // tile `buf` may be refilled
     }
+    if (threadIdx.x == 0 && *abort_flag) report_status(p.status, MOK_STATUS_PIPELINE_TIMEOUT, 210);
 }
 
 int launch_dispatch_quant(const RowMoveParams& p, const QuantOut& out, bool scale, int num_blocks, cudaStream_t stream) {
@@ -279,14 +347,14 @@ int launch_dispatch_quant(const RowMoveParams& p, const QuantOut& out, bool scal
 
 int launch_dispatch_rows(const RowMoveParams& p, bool scale, int num_blocks, cudaStream_t stream) {
     ProfScope prof(kSlotDispatch, stream);
-    if (scale) dispatch_rows_kernel<true><<<num_blocks, 256, 0, stream>>>(p);
-    else dispatch_rows_kernel<false><<<num_blocks, 256, 0, stream>>>(p);
+    if (scale) move_rows_kernel<kMoveDispatchScale><<<num_blocks, kMoveWarps * 32, 0, stream>>>(p);
+    else move_rows_kernel<kMoveDispatch><<<num_blocks, kMoveWarps * 32, 0, stream>>>(p);
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
 }
 int launch_combine_rows(const RowMoveParams& p, int num_blocks, cudaStream_t stream) {
     ProfScope prof(kSlotCombine, stream);
-    combine_rows_kernel<<<num_blocks, 256, 0, stream>>>(p);
+    move_rows_kernel<kMoveCombine><<<num_blocks, kMoveWarps * 32, 0, stream>>>(p);
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
 }

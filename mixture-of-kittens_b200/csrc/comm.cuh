@@ -25,6 +25,7 @@ struct RowMoveParams {
     float* row_scale_out;      // dispatch<scale>: [row_limit] router weight of every routed row
     const float* partials;     // combine: [row_limit, partial_cols] router-gradient partial sums
     int partial_cols;
+    int* status;               // device status word (bounded waits report here)
 };
 
 int launch_dispatch_rows(const RowMoveParams& p, bool scale, int num_blocks, cudaStream_t stream);

@@ -181,6 +181,7 @@ RowMoveParams row_move(const mok_layer_common& c, const Dims& d, int off, int li
     r.row_limit = limit;
     r.hidden = d.H;
     r.row_divisor = 1;
+    r.status = c.status;
     r.chunk = t_chunk;
     return r;
 }
@@ -297,17 +298,20 @@ int move_grid() {
         const char* e = std::getenv("MOK_B200_COMM_BLOCKS");
         return e ? std::atoi(e) : 0;
     }();
-    return configured > 0 ? configured : device_sm_count() * 2;
+    return configured > 0 ? configured : device_sm_count() * 4;
 }
 
 int pipeline_chunks(const mok_layer_common& c, int limit) {
     static const int configured = [] {
         const char* e = std::getenv("MOK_B200_CHUNKS");
-        const int v = e ? std::atoi(e) : 1;
-        return v < 1 ? 1 : (v > 32 ? 32 : v);
+        const int v = e ? std::atoi(e) : 0;
+        return v < 0 ? 0 : (v > 32 ? 32 : v);
     }();
+    // default: no chunking on a single rank (movement and GEMMs compete for HBM there), eight chunks
+    // when rows cross NVLink
+    const int want = configured > 0 ? configured : (c.ep_size > 1 ? 8 : 1);
     const int by_minibatch = limit / c.minibatch_size;
-    return std::max(1, std::min(configured, by_minibatch));
+    return std::max(1, std::min(want, by_minibatch));
 }
 
 }  // namespace
