@@ -114,8 +114,7 @@ __global__ void __launch_bounds__(256) epilogue_kernel(const uint4* __restrict__
 // set by the slots (24 KB per CTA), not by registers.  Remote addresses are plain unicast peer
 // mappings; no multicast.
 enum : int { kMoveDispatch = 0, kMoveDispatchScale = 1, kMoveCombine = 2 };
-constexpr int kMoveWarps = 3;
-constexpr int kMovePiece = 4096;
+constexpr int kMoveMaxWarps = 8;
 
 __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
@@ -128,9 +127,11 @@ __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, u
 }
 
 template <int kMode>
-__global__ void __launch_bounds__(kMoveWarps * 32) move_rows_kernel(RowMoveParams p) {
-    __shared__ __align__(128) uint8_t slots[kMoveWarps][2][kMovePiece];
-    __shared__ __align__(8) uint64_t bars[kMoveWarps][2];
+__global__ void __launch_bounds__(kMoveMaxWarps * 32) move_rows_kernel(RowMoveParams p) {
+    extern __shared__ __align__(128) uint8_t slot_mem[];      // [warps][2][piece]
+    __shared__ __align__(8) uint64_t bars[kMoveMaxWarps][2];
+    const int kMoveWarps = static_cast<int>(blockDim.x >> 5);
+    const int kMovePiece = p.piece_bytes;
     __shared__ int abort_word;
     volatile int* abort_flag = &abort_word;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -190,7 +191,7 @@ __global__ void __launch_bounds__(kMoveWarps * 32) move_rows_kernel(RowMoveParam
             // the slot was last read by the store committed in the previous iteration
             if (issued >= 2) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
             mbar_arrive_expect_tx(&bars[warp][slot], bytes_n);
-            bulk_g2s(slots[warp][slot], src_n, bytes_n, &bars[warp][slot]);
+            bulk_g2s((slot_mem + (static_cast<size_t>(warp) * 2 + slot) * kMovePiece), src_n, bytes_n, &bars[warp][slot]);
         }
         if (live_n) ++issued;
     };
@@ -213,7 +214,7 @@ __global__ void __launch_bounds__(kMoveWarps * 32) move_rows_kernel(RowMoveParam
         if (!mbar_wait(&bars[warp][slot], phase[slot], abort_flag)) { ok = false; break; }
         phase[slot] ^= 1;
         if (kMode == kMoveDispatchScale) {
-            uint4* s4 = reinterpret_cast<uint4*>(slots[warp][slot]);
+            uint4* s4 = reinterpret_cast<uint4*>((slot_mem + (static_cast<size_t>(warp) * 2 + slot) * kMovePiece));
             for (uint32_t v = lane; v < bytes / 16; v += 32) {
                 uint4 q = s4[v];
                 uint32_t* w32 = reinterpret_cast<uint32_t*>(&q);
@@ -225,7 +226,7 @@ __global__ void __launch_bounds__(kMoveWarps * 32) move_rows_kernel(RowMoveParam
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
         }
-        if (lane == 0) bulk_s2g(dst, slots[warp][slot], bytes);
+        if (lane == 0) bulk_s2g(dst, (slot_mem + (static_cast<size_t>(warp) * 2 + slot) * kMovePiece), bytes);
         if (kMode == kMoveCombine && p.partials != nullptr && piece == 0 && lane == 0) {
             float s = 0.0f;
             for (int c = 0; c < p.partial_cols; ++c) s += p.partials[static_cast<size_t>(row) * p.partial_cols + c];
@@ -345,16 +346,36 @@ int launch_dispatch_quant(const RowMoveParams& p, const QuantOut& out, bool scal
     return MOK_OK;
 }
 
+// Two shapes of mover CTA: "thin" (3 warps x 2 x 4 KB = 24 KB, many CTAs, fits beside a GEMM CTA) and
+// "fat" (8 warps x 2 x 8 KB = 128 KB, a few CTAs that each take an SM of their own).
+template <int kMode>
+int launch_move(RowMoveParams p, int num_blocks, cudaStream_t stream) {
+    const bool fat = p.fat_ctas != 0;
+    const int warps = fat ? 8 : 3;
+    p.piece_bytes = fat ? 8192 : 4096;
+    const int smem = warps * 2 * p.piece_bytes;
+    static bool configured[64] = {false};
+    int dev = 0;
+    MOK_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev]) {
+        MOK_CUDA_CHECK(cudaFuncSetAttribute(move_rows_kernel<kMode>, cudaFuncAttributeMaxDynamicSharedMemorySize, 8 * 2 * 8192));
+        if (dev >= 0 && dev < 64) configured[dev] = true;
+    }
+    move_rows_kernel<kMode><<<num_blocks, warps * 32, smem, stream>>>(p);
+    MOK_CUDA_CHECK(cudaGetLastError());
+    return MOK_OK;
+}
+
 int launch_dispatch_rows(const RowMoveParams& p, bool scale, int num_blocks, cudaStream_t stream) {
     ProfScope prof(kSlotDispatch, stream);
-    if (scale) move_rows_kernel<kMoveDispatchScale><<<num_blocks, kMoveWarps * 32, 0, stream>>>(p);
-    else move_rows_kernel<kMoveDispatch><<<num_blocks, kMoveWarps * 32, 0, stream>>>(p);
+    if (scale) return launch_move<kMoveDispatchScale>(p, num_blocks, stream);
+    return launch_move<kMoveDispatch>(p, num_blocks, stream);
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
 }
 int launch_combine_rows(const RowMoveParams& p, int num_blocks, cudaStream_t stream) {
     ProfScope prof(kSlotCombine, stream);
-    move_rows_kernel<kMoveCombine><<<num_blocks, kMoveWarps * 32, 0, stream>>>(p);
+    return launch_move<kMoveCombine>(p, num_blocks, stream);
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
 }

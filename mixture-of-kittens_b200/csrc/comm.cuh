@@ -26,6 +26,8 @@ struct RowMoveParams {
     const float* partials;     // combine: [row_limit, partial_cols] router-gradient partial sums
     int partial_cols;
     int* status;               // device status word (bounded waits report here)
+    int fat_ctas;              // 1: few CTAs with 128 KB of copy slots each (dedicated SMs); 0: many thin CTAs
+    int piece_bytes;           // set by the launcher
 };
 
 int launch_dispatch_rows(const RowMoveParams& p, bool scale, int num_blocks, cudaStream_t stream);

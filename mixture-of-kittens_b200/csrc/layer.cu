@@ -47,6 +47,8 @@ int fill_peers(PeerPtrs& out, const uint64_t* ptrs, int W) {
 
 // row sub-range the helpers below put into every routed launch they build (set by the pipeline)
 thread_local ChunkSpec t_chunk = {0, 1, 0};
+thread_local int t_gemm_ctas = 0;     // cap on the CTAs of routed GEMM launches inside the pipeline (0 = all SMs)
+thread_local int t_fat_movers = 0;    // movers run as a few fat CTAs on SMs of their own
 
 GemmParams base_params(const mok_layer_common& c, bool routed, int off, int limit) {
     GemmParams p{};
@@ -87,7 +89,7 @@ int run_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int off, 
     o.a0 = a; o.b0 = wg; o.b1 = wu;
     o.a_inner = d.H; o.a_outer = a_rows;
     o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.I;
-    return launch_grouped_gemm(kMajorK, kMajorK, kEpiSwigluFwd, false, o, p, (limit / kBlockM) * p.n_tiles, 0,
+    return launch_grouped_gemm(kMajorK, kMajorK, kEpiSwigluFwd, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? t_gemm_ctas : 0,
                                routed ? kSlotGateUpRouted : kSlotGateUpShared, s);
 }
 
@@ -104,7 +106,7 @@ int run_down(const mok_layer_common& c, const Dims& d, bool routed, int off, int
     o.a0 = hidden; o.b0 = wd;
     o.a_inner = d.I; o.a_outer = a_rows;
     o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.H;
-    return launch_grouped_gemm(kMajorK, kMajorK, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0,
+    return launch_grouped_gemm(kMajorK, kMajorK, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? t_gemm_ctas : 0,
                                routed ? kSlotDownRouted : kSlotDownShared, s);
 }
 
@@ -128,7 +130,7 @@ int run_dgrad_down(const mok_layer_common& c, const Dims& d, bool routed, int of
     o.a0 = d_y; o.b0 = wd;
     o.a_inner = d.H; o.a_outer = a_rows;
     o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.H;
-    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiSwigluBwd, false, o, p, (limit / kBlockM) * p.n_tiles, 0,
+    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiSwigluBwd, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? t_gemm_ctas : 0,
                                routed ? kSlotDgradDownRouted : kSlotDgradDownShared, s);
 }
 
@@ -146,7 +148,7 @@ int run_dgrad_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int
     o.a0 = d_gate; o.a1 = d_up; o.b0 = wg; o.b1 = wu;
     o.a_inner = d.I; o.a_outer = a_rows;
     o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.I;
-    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0,
+    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? t_gemm_ctas : 0,
                                routed ? kSlotDgradGateUpRouted : kSlotDgradGateUpShared, s);
 }
 
@@ -182,6 +184,7 @@ RowMoveParams row_move(const mok_layer_common& c, const Dims& d, int off, int li
     r.hidden = d.H;
     r.row_divisor = 1;
     r.status = c.status;
+    r.fat_ctas = t_fat_movers;
     r.chunk = t_chunk;
     return r;
 }
@@ -208,6 +211,16 @@ struct DeviceStreams {
 };
 DeviceStreams g_streams[64];
 std::mutex g_streams_mu;
+
+// SMs set aside for the movers while a window is processed in chunks (0 = movers share SMs with the GEMMs)
+int comm_sm_count() {
+    static const int configured = [] {
+        const char* e = std::getenv("MOK_B200_COMM_SMS");
+        const int v = e ? std::atoi(e) : 0;
+        return v < 0 ? 0 : (v > 64 ? 64 : v);
+    }();
+    return configured;
+}
 
 class Pipeline {
 public:
@@ -245,6 +258,8 @@ public:
             return store(main_);
         }
         int rc = MOK_OK;
+        const int comm_sms = comm_sm_count();
+        if (comm_sms > 0) { t_gemm_ctas = device_sm_count() - comm_sms; t_fat_movers = 1; }
         std::vector<cudaEvent_t> loaded(chunks_);
         set_chunk(0);
         if ((rc = load(ds_->side))) return finish(rc);
@@ -268,7 +283,7 @@ public:
 
 private:
     void set_chunk(int c) { t_chunk = ChunkSpec{c, chunks_, min_rows_}; }
-    int finish(int rc) { t_chunk = ChunkSpec{0, 1, 0}; return rc; }
+    int finish(int rc) { t_chunk = ChunkSpec{0, 1, 0}; t_gemm_ctas = 0; t_fat_movers = 0; return rc; }
     int record(cudaStream_t s, cudaEvent_t& out) {
         std::lock_guard<std::mutex> lock(g_streams_mu);
         if (next_ == ds_->events.size()) {
@@ -293,7 +308,9 @@ private:
 };
 
 // CTAs of a row-movement launch.  Inside the pipeline they share the SMs with the persistent GEMM CTAs.
-int move_grid() {
+int move_grid_thin();
+int move_grid() { return t_fat_movers ? comm_sm_count() : move_grid_thin(); }
+int move_grid_thin() {
     static const int configured = [] {
         const char* e = std::getenv("MOK_B200_COMM_BLOCKS");
         return e ? std::atoi(e) : 0;
@@ -329,7 +346,6 @@ extern "C" int mok_fwd_bf16(const mok_fwd_bf16_args* a, void* stream) {
     MOK_TRY(fill_peers(x_peers, a->x_ptrs, d.W));
     MOK_TRY(fill_peers(combine_peers, a->combine_buffer_ptrs, d.W));
     const void* x_local = x_peers.p[d.rank];
-    const int move_blocks = move_grid();
     Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
     MOK_TRY(pipe.error());
     MOK_TRY(pipe.fork());
@@ -348,7 +364,7 @@ extern "C" int mok_fwd_bf16(const mok_fwd_bf16_args* a, void* stream) {
                 RowMoveParams disp = row_move(c, d, off, limit, a->x_routed);
                 disp.peers = x_peers;
                 disp.row_divisor = d.K;
-                return launch_dispatch_rows(disp, false, move_blocks, st);
+                return launch_dispatch_rows(disp, false, move_grid(), st);
             },
             [&](cudaStream_t st) {
                 MOK_TRY(run_gate_up(c, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up,
@@ -358,7 +374,7 @@ extern "C" int mok_fwd_bf16(const mok_fwd_bf16_args* a, void* stream) {
             [&](cudaStream_t st) {
                 RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
                 comb.peers = combine_peers;
-                return launch_combine_rows(comb, move_blocks, st);
+                return launch_combine_rows(comb, move_grid(), st);
             }));
         MOK_TRY(pipe.join());      // the next window reuses the buffers
         if (m > 0) MOK_TRY(pipe.fork());
@@ -381,7 +397,6 @@ extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
     if (!a->router_weights_routed || !a->d_router_weight_partials) return MOK_ERR_INVALID;
     const void* dy_local = dy_peers.p[d.rank];
     const void* x_local = x_peers.p[d.rank];
-    const int move_blocks = move_grid();
     const int partial_cols = d.I / kBlockN;
     Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
     MOK_TRY(pipe.error());
@@ -404,7 +419,7 @@ extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
             RowMoveParams disp = row_move(c, d, off, limit, a->x_routed);
             disp.peers = x_peers;
             disp.row_divisor = d.K;
-            MOK_TRY(launch_dispatch_rows(disp, false, move_blocks, s));
+            MOK_TRY(launch_dispatch_rows(disp, false, move_grid(), s));
             MOK_TRY(run_gate_up(c, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up, a->gate_routed,
                                 a->up_routed, a->hidden_routed, s));
             MOK_TRY(pipe.fork());
@@ -416,7 +431,7 @@ extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
                 rc.scale_peers = rw_peers;
                 rc.row_divisor = d.K;
                 rc.row_scale_out = a->router_weights_routed;
-                return launch_dispatch_rows(rc, true, move_blocks, st);
+                return launch_dispatch_rows(rc, true, move_grid(), st);
             },
             [&](cudaStream_t st) {
                 MOK_TRY(run_dgrad_down(c, d, true, off, limit, a->d_y_routed, d.MB, a->w_routed_down, a->gate_routed,
@@ -431,7 +446,7 @@ extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
                 rd.scale_peers = drw_peers;
                 rd.partials = a->d_router_weight_partials;
                 rd.partial_cols = partial_cols;
-                return launch_combine_rows(rd, move_blocks, st);
+                return launch_combine_rows(rd, move_grid(), st);
             }));
         MOK_TRY(pipe.join());
         const int acc = m > 0 ? 1 : 0;
@@ -506,7 +521,7 @@ int mx_gate_up(const mok_layer_common& c, const Dims& d, int off, int limit, con
     o.a0 = x_q; o.b0 = wg_q; o.b1 = wu_q;
     o.a_inner = d.H; o.a_outer = d.MB;
     o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(d.El) * d.I;
-    return launch_mx_gemm(kMxEpiGateUp, false, o, p, (limit / kBlockM) * p.n_tiles, 0, kSlotGateUpRouted, s);
+    return launch_mx_gemm(kMxEpiGateUp, false, o, p, (limit / kBlockM) * p.n_tiles, t_gemm_ctas, kSlotGateUpRouted, s);
 }
 
 int mx_down(const mok_layer_common& c, const Dims& d, int off, int limit, const void* hid_q, const void* hid_sc,
@@ -523,7 +538,7 @@ int mx_down(const mok_layer_common& c, const Dims& d, int off, int limit, const 
     o.a0 = hid_q; o.b0 = wd_q;
     o.a_inner = d.I; o.a_outer = d.MB;
     o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(d.El) * d.H;
-    return launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0, kSlotDownRouted, s);
+    return launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, t_gemm_ctas, kSlotDownRouted, s);
 }
 
 int mx_wgrad(const mok_layer_common& c, const Dims& d, int off, int limit, const void* a_qt, const void* a_sct, int m,
@@ -557,7 +572,6 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
     MOK_TRY(fill_peers(x_peers, a->x_ptrs, d.W));
     MOK_TRY(fill_peers(combine_peers, a->combine_buffer_ptrs, d.W));
     const void* x_local = x_peers.p[d.rank];
-    const int move_blocks = move_grid();
     Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
     MOK_TRY(pipe.error());
     MOK_TRY(pipe.fork());
@@ -576,7 +590,7 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
                 disp.peers = x_peers;
                 disp.row_divisor = d.K;
                 QuantOut xo{u8(a->work_x_q), u8(a->work_x_sc), u8(a->x_qt), u8(a->x_sct), d.MB};
-                return launch_dispatch_quant(disp, xo, false, move_blocks, st);
+                return launch_dispatch_quant(disp, xo, false, move_grid(), st);
             },
             [&](cudaStream_t st) {
                 MOK_TRY(mx_gate_up(c, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
@@ -588,7 +602,7 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
             [&](cudaStream_t st) {
                 RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
                 comb.peers = combine_peers;
-                return launch_combine_rows(comb, move_blocks, st);
+                return launch_combine_rows(comb, move_grid(), st);
             }));
         MOK_TRY(pipe.join());
         if (m > 0) MOK_TRY(pipe.fork());
@@ -611,7 +625,6 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
     if (!a->router_weights_routed || !a->d_router_weight_partials) return MOK_ERR_INVALID;
     const void* dy_local = dy_peers.p[d.rank];
     const void* x_local = x_peers.p[d.rank];
-    const int move_blocks = move_grid();
     const int partial_cols = d.I / kBlockN;
     Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
     MOK_TRY(pipe.error());
@@ -635,7 +648,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
             disp.peers = x_peers;
             disp.row_divisor = d.K;
             QuantOut xo{u8(a->work_x_q), u8(a->work_x_sc), u8(a->x_qt), u8(a->x_sct), d.MB};
-            MOK_TRY(launch_dispatch_quant(disp, xo, false, move_blocks, s));
+            MOK_TRY(launch_dispatch_quant(disp, xo, false, move_grid(), s));
             MOK_TRY(mx_gate_up(c, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
                                a->w_routed_up_q, a->w_routed_up_sc, a->gate_q, a->gate_sc, a->up_q, a->up_sc,
                                a->work_hidden_q, a->work_hidden_sc, a->hidden_qt, a->hidden_sct, s));
@@ -649,7 +662,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                 rc.row_divisor = d.K;
                 rc.row_scale_out = a->router_weights_routed;
                 QuantOut dyo{u8(a->d_y_q), u8(a->d_y_sc), u8(a->work_d_y_qt), u8(a->work_d_y_sct), d.MB};
-                return launch_dispatch_quant(rc, dyo, true, move_blocks, st);
+                return launch_dispatch_quant(rc, dyo, true, move_grid(), st);
             },
             [&](cudaStream_t st) {
                 {   // d_hidden = d_y @ Wd (weights pre-transposed to [El, I, H]) + SwiGLU backward
@@ -673,7 +686,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                     o.a0 = a->d_y_q; o.b0 = a->w_routed_down_T_q;
                     o.a_inner = d.H; o.a_outer = d.MB;
                     o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(d.El) * d.I;
-                    MOK_TRY(launch_mx_gemm(kMxEpiDgradDown, false, o, p, (limit / kBlockM) * p.n_tiles, 0,
+                    MOK_TRY(launch_mx_gemm(kMxEpiDgradDown, false, o, p, (limit / kBlockM) * p.n_tiles, t_gemm_ctas,
                                            kSlotDgradDownRouted, st));
                 }
                 // d_x = d_gate @ Wg + d_up @ Wu (weights pre-transposed to [El, H, I]) in one accumulator
@@ -690,7 +703,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                 o.a0 = a->d_gate_q; o.a1 = a->d_up_q; o.b0 = a->w_routed_gate_T_q; o.b1 = a->w_routed_up_T_q;
                 o.a_inner = d.I; o.a_outer = d.MB;
                 o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(d.El) * d.H;
-                return launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, 0, kSlotDgradGateUpRouted, st);
+                return launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, t_gemm_ctas, kSlotDgradGateUpRouted, st);
             },
             [&](cudaStream_t st) {
                 RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
@@ -698,7 +711,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                 rd.scale_peers = drw_peers;
                 rd.partials = a->d_router_weight_partials;
                 rd.partial_cols = 2 * partial_cols   /* the MXFP8 epilogue writes one partial per 128-column half */;
-                return launch_combine_rows(rd, move_blocks, st);
+                return launch_combine_rows(rd, move_grid(), st);
             }));
         MOK_TRY(pipe.join());
         const int acc = m > 0 ? 1 : 0;
