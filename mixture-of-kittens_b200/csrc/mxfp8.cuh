@@ -11,10 +11,13 @@
 
 namespace mok {
 
+// Conversions use the hardware converters (cvt.rp.satfinite.ue8m0x2, cvt.rn.satfinite.e4m3x2, fp8x2 ->
+// f16x2): two values per instruction.  An all-integer formulation of the same roundings was measured
+// and was slower in every kernel here (the kernels are issue-bound, not converter-bound).
 __device__ __forceinline__ uint32_t mx_scale_byte(float amax) {
     const float scale = fmaxf(amax * 0.002232142857f, 0.000000000001f);
     uint16_t sc2;
-    asm volatile("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(sc2) : "f"(scale), "f"(scale));
+    asm("cvt.rp.satfinite.ue8m0x2.f32 %0, %1, %2;" : "=h"(sc2) : "f"(scale), "f"(scale));
     return sc2 & 0xFFu;
 }
 __device__ __forceinline__ float mx_inv_scale(uint32_t scale_byte) {
@@ -23,7 +26,7 @@ __device__ __forceinline__ float mx_inv_scale(uint32_t scale_byte) {
 // two floats -> two E4M3 bytes, `lo` in the low byte
 __device__ __forceinline__ uint32_t mx_pack2(float lo, float hi) {
     uint16_t r;
-    asm volatile("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(r) : "f"(lo), "f"(hi));
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %2, %1;" : "=h"(r) : "f"(lo), "f"(hi));
     return r;
 }
 __device__ __forceinline__ uint32_t mx_pack4(float a, float b, float c, float d) {

@@ -391,7 +391,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                             gf.x = fminf(gf.x, p.limit); gf.y = fminf(gf.y, p.limit);
                             uf.x = fminf(fmaxf(uf.x, -p.limit), p.limit); uf.y = fminf(fmaxf(uf.y, -p.limit), p.limit);
                         }
-                        const float s0 = __fdividef(1.0f, 1.0f + __expf(-gf.x)), s1 = __fdividef(1.0f, 1.0f + __expf(-gf.y));
+                        const float s0 = sigmoid_fast(gf.x), s1 = sigmoid_fast(gf.y);
                         const float silu0 = gf.x * s0, silu1 = gf.y * s1;
                         const float ds0 = (1.0f - silu0) * s0 + silu0, ds1 = (1.0f - silu1) * s1 + silu1;
                         dg[i] = pack_bf16(gm0 ? ds0 * uf.x * dhf.x : 0.0f, gm1 ? ds1 * uf.y * dhf.y : 0.0f);

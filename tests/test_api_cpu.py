@@ -1,0 +1,120 @@
+"""CPU: the Python boundary mirrors the reference's operator/functional interface — names, defaults,
+exception classes raised before any launch, FakeTensor shape propagation, mutation schemas
+(reference: mok/functional.py:22-48, mok/ops.py validation blocks, tests/test_misc.py:582-1043)."""
+import dataclasses
+
+import pytest
+import torch
+from torch._subclasses.fake_tensor import FakeTensorMode
+
+
+def test_config_defaults_and_dataclasses():
+    import mok
+    F = mok.functional
+    cfg = F.MoKConfig()
+    assert dataclasses.asdict(cfg) == dict(fwd_num_comm_sms=40, bwd_num_comm_sms=28, minibatch_size=4096,
+                                           macrobatch_size=131072, schedule_capacity_multiplier=0.5,
+                                           all_gather_top_experts_chunk_bytes=2048)
+    with pytest.raises(dataclasses.FrozenInstanceError):
+        cfg.minibatch_size = 1
+    assert [f.name for f in dataclasses.fields(F.MoKSchedule)] == ["peer_rank", "peer_token_idx", "num_tokens",
+                                                                   "tokens_per_expert"]
+    assert [f.name for f in dataclasses.fields(F.MoKForwardContext)] == [
+        "x_routed", "gate_shared", "gate_routed", "up_shared", "up_routed", "hidden_shared", "hidden_routed"]
+    assert len(dataclasses.fields(F.MoKWorkspace)) == 34
+    assert F.schedule is F.build_schedule
+    assert mok.__version__ == "0.1.0"
+
+
+def test_ten_operators_are_registered():
+    import mok  # noqa: F401
+    names = ["all_gather_top_experts", "barrier_all", "schedule", "mxfp8_quantize",
+             "dispatch_mlp_swiglu_combine_fwd_mxfp8", "dispatch_mlp_swiglu_combine_fwd_bf16",
+             "dispatch_mlp_swiglu_combine_bwd_mxfp8", "dispatch_mlp_swiglu_combine_bwd_bf16",
+             "fwd_epilogue", "bwd_epilogue"]
+    for n in names:
+        assert hasattr(torch.ops.mok, n), n
+
+
+def test_mutation_schemas():
+    import mok  # noqa: F401
+    def mutated(op):
+        return {a.name for a in op.default._schema.arguments if a.alias_info is not None and a.alias_info.is_write}
+    assert mutated(torch.ops.mok.all_gather_top_experts) == {"all_gather_top_experts_buffer"}
+    assert mutated(torch.ops.mok.barrier_all) == {"barrier_buffer", "target"}
+    assert mutated(torch.ops.mok.schedule) == set()
+    assert mutated(torch.ops.mok.dispatch_mlp_swiglu_combine_fwd_bf16) == {"combine_buffer"}
+    assert mutated(torch.ops.mok.dispatch_mlp_swiglu_combine_bwd_bf16) == {
+        "d_x_routed_buffer", "d_router_weight_buffer", "x_routed", "gate_routed", "up_routed", "hidden_routed"}
+    assert mutated(torch.ops.mok.dispatch_mlp_swiglu_combine_bwd_mxfp8) == {
+        "d_x_routed_buffer", "d_router_weight_buffer", "x_fp8_t_routed", "x_sc_t_routed", "gate_fp8_routed",
+        "gate_sc_routed", "up_fp8_routed", "up_sc_routed", "hidden_fp8_t_routed", "hidden_sc_t_routed"}
+
+
+def test_argument_errors_are_raised_before_any_launch():
+    import mok
+    ops = mok.ops
+    i32 = torch.int32
+    with pytest.raises(ValueError):
+        ops.schedule(torch.zeros(3, 512, 2, dtype=i32), 4, 4096, 0)            # ep size 3
+    with pytest.raises(ValueError):
+        ops.schedule(torch.zeros(4, 500, 2, dtype=i32), 4, 4096, 0)            # tokens not a multiple of 256
+    with pytest.raises(ValueError):
+        ops.schedule(torch.zeros(4, 512, 2, dtype=i32), 4, 1000, 0)            # capacity not a multiple of 256
+    with pytest.raises(ValueError):
+        ops.schedule(torch.zeros(4, 512, 2, dtype=i32), 4, 512, 0)             # capacity below one rank's routes
+    with pytest.raises(ValueError):
+        ops.schedule(torch.zeros(4, 512, 2, dtype=i32), 4, 4096, 4)            # rank out of range
+    with pytest.raises(ValueError):
+        ops.mxfp8_quantize(torch.zeros(100, 128, dtype=torch.bfloat16), True, False)
+    with pytest.raises(TypeError):
+        ops.mxfp8_quantize(torch.zeros(128, 128, dtype=torch.bfloat16), 1, False)
+    with pytest.raises(ValueError):
+        ops.mxfp8_quantize(torch.zeros(128, 128, dtype=torch.bfloat16), False, False)
+    with pytest.raises(ValueError):
+        ops.fwd_epilogue(torch.zeros(500, 256, dtype=torch.bfloat16), torch.zeros(1000, 256, dtype=torch.bfloat16),
+                         torch.zeros(500, 2))
+    with pytest.raises(ValueError):
+        ops.bwd_epilogue(torch.zeros(512, 256, dtype=torch.bfloat16), torch.zeros(700, 256, dtype=torch.bfloat16))
+    with pytest.raises(ValueError):
+        ops.barrier_all(torch.zeros(1, dtype=i32), [1, 2, 3, 4], 0, torch.zeros(1, dtype=i32))   # not a CUDA buffer
+    with pytest.raises(ValueError):
+        ops.all_gather_top_experts(torch.zeros(512, 2, dtype=i32), torch.zeros(4, 512, 2, dtype=i32), 0, 0, 2048)
+
+
+def test_fake_tensor_shapes():
+    import mok
+    ops = mok.ops
+    T, H, I, El, K, MB, cap, W = 512, 256, 512, 4, 2, 1024, 2048, 4
+    with FakeTensorMode():
+        dev = "cuda"
+        bf = lambda *s: torch.empty(*s, dtype=torch.bfloat16, device=dev)          # noqa: E731
+        f8 = lambda *s: torch.empty(*s, dtype=torch.float8_e4m3fn, device=dev)     # noqa: E731
+        u8 = lambda *s: torch.empty(*s, dtype=torch.uint8, device=dev)             # noqa: E731
+        i32 = lambda *s: torch.empty(*s, dtype=torch.int32, device=dev)            # noqa: E731
+        sc = lambda r, c: u8(r // 128, c // 128, 32, 16)                           # noqa: E731
+        ptrs = [1, 2, 3, 4]
+        sched = (i32(cap), i32(cap), i32(1), i32(El))
+        out = ops.schedule(i32(W, T, K), El, cap, 0)
+        assert [tuple(t.shape) for t in out] == [(cap,), (cap,), (1,), (El,)]
+        q = ops.mxfp8_quantize(bf(El, I, H), True, True)
+        assert tuple(q[0].shape) == (El, I, H) and tuple(q[1].shape) == (El * I // 128, H // 128, 32, 16)
+        assert tuple(q[2].shape) == (El, H, I) and tuple(q[3].shape) == (El * H // 128, I // 128, 32, 16)
+        assert ops.mxfp8_quantize(bf(I, H), True, False)[2] is None
+        fwd = ops.dispatch_mlp_swiglu_combine_fwd_bf16(bf(T, H), ptrs, bf(T * K, H), ptrs, bf(I, H), bf(El, I, H), bf(I, H),
+                                                       bf(El, I, H), bf(H, I), bf(El, H, I), *sched, K, None, 40, MB, 256)
+        assert [tuple(t.shape) for t in fwd] == [(MB, H), (T, I), (MB, I), (T, I), (MB, I), (T, I), (MB, I), (T, H), (MB, H)]
+        fwd8 = ops.dispatch_mlp_swiglu_combine_fwd_mxfp8(
+            bf(T, H), ptrs, bf(T * K, H), ptrs, bf(I, H), f8(El, I, H), sc(El * I, H), bf(I, H), f8(El, I, H), sc(El * I, H),
+            bf(H, I), f8(El, H, I), sc(El * H, I), *sched, K, 4.0, 40, MB, 256)
+        assert [tuple(t.shape) for t in fwd8] == [(H, MB), (H // 128, MB // 128, 32, 16), (T, I), (MB, I),
+                                                  (MB // 128, I // 128, 32, 16), (T, I), (MB, I), (MB // 128, I // 128, 32, 16),
+                                                  (T, I), (I, MB), (I // 128, MB // 128, 32, 16), (T, H), (MB, H)]
+        assert fwd8[0].dtype == torch.float8_e4m3fn and fwd8[1].dtype == torch.uint8 and fwd8[12].dtype == torch.bfloat16
+        bwd = ops.dispatch_mlp_swiglu_combine_bwd_bf16(
+            bf(T, H), ptrs, bf(T * K, H), ptrs, torch.empty(T, K, device=dev), ptrs, torch.empty(T, K, device=dev), ptrs,
+            bf(I, H), bf(El, I, H), bf(I, H), bf(El, I, H), bf(H, I), bf(El, H, I),
+            bf(MB, H), bf(T, I), bf(MB, I), bf(T, I), bf(MB, I), bf(T, I), bf(MB, I), bf(T, H), ptrs, *sched, K, None, 28, MB, 256)
+        assert len(bwd) == 15 and tuple(bwd[10].shape) == (El, I, H) and tuple(bwd[14].shape) == (El, H, I)
+        assert tuple(ops.fwd_epilogue(bf(T, H), bf(T * K, H), torch.empty(T, K, device=dev)).shape) == (T, H)
+        assert tuple(ops.bwd_epilogue(bf(T, H), bf(T * K, H)).shape) == (T, H)
