@@ -220,7 +220,7 @@ typedef struct mok_bwd_mxfp8_args {
     void *work_x_q, *work_x_sc, *work_hidden_q, *work_hidden_sc;           /* replay */
     void *work_d_y_qt, *work_d_y_sct, *work_d_gate_qt, *work_d_gate_sct, *work_d_up_qt, *work_d_up_sct;
     float* router_weights_routed;                                          /* [MB] */
-    float* d_router_weight_partials;                                       /* [MB, I/128] */
+    float* d_router_weight_partials;                                       /* [MB, I/64] */
 } mok_bwd_mxfp8_args;
 int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* args, void* stream);
 

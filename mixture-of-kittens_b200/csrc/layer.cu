@@ -710,7 +710,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                 rd.peers = dxr_peers;
                 rd.scale_peers = drw_peers;
                 rd.partials = a->d_router_weight_partials;
-                rd.partial_cols = 2 * partial_cols   /* the MXFP8 epilogue writes one partial per 128-column half */;
+                rd.partial_cols = 4 * partial_cols   /* the MXFP8 epilogue writes one partial per 64-column slice */;
                 return launch_combine_rows(rd, move_grid(), st);
             }));
         MOK_TRY(pipe.join());

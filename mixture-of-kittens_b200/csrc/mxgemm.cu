@@ -11,10 +11,10 @@ int launch_mx_inst(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorM
     int dev = 0;
     MOK_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
-        MOK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kMxSmemBytes));
+        MOK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, mx_smem_bytes(kEpi)));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kern<<<grid, kMxThreads, kMxSmemBytes, stream>>>(a0, b0, a1, b1, p);
+    kern<<<grid, kMxThreads, mx_smem_bytes(kEpi), stream>>>(a0, b0, a1, b1, p);
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
 }

@@ -35,9 +35,15 @@ constexpr int kMxABytes = kBlockM * kMxBlockK;        // 16 KB
 constexpr int kMxBBytes = kBlockN * kMxBlockK;        // 32 KB
 constexpr int kMxTileBytes = kMxABytes + kMxBBytes;
 constexpr int kMxSfBytes = 512 + 1024;                // A scales + B scales per stage
-constexpr int kMxThreads = 64 + 256;                  // producer warp, MMA warp, eight epilogue warps
-constexpr int kMxTrBytes = 8 * 32 * 17 * 4;           // per-epilogue-warp transpose tiles
-constexpr int kMxSmemBytes = kStages * (kMxTileBytes + kMxSfBytes) + 256 + kMaxExperts * 4 + kMxTrBytes + 1024;
+// pipeline depth: 4 stages for the plain-store epilogue, 3 where the epilogue needs transpose tiles in shared memory
+__host__ __device__ constexpr int mx_stages(int epi) { return epi == 0 ? 4 : 3; }
+constexpr int kMxEpiGroups = 4;                       // epilogue warps per TMEM lane quarter (each takes 64 of the 256 columns)
+constexpr int kMxEpiWarps = 4 * kMxEpiGroups;
+constexpr int kMxThreads = 64 + 32 * kMxEpiWarps;     // producer warp, MMA warp, sixteen epilogue warps
+constexpr int kMxTrBytes = kMxEpiWarps * 32 * 17 * 4; // per-epilogue-warp transpose tiles
+__host__ __device__ constexpr int mx_smem_bytes(int epi) {
+    return mx_stages(epi) * (kMxTileBytes + kMxSfBytes) + 256 + kMaxExperts * 4 + (epi == 0 ? 0 : kMxTrBytes) + 1024;
+}
 constexpr int kMxAccCols = 256, kMxSfaCol = 256, kMxSfbCol = 260;
 
 struct MxGemmParams {
@@ -124,17 +130,18 @@ __global__ void __launch_bounds__(kMxThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                const MxGemmParams p) {
+    constexpr int kMxStages = mx_stages(kEpi);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* sf_smem = smem + kStages * kMxTileBytes;
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(sf_smem + kStages * kMxSfBytes);
-    uint64_t* empty_bar = full_bar + kStages;
-    uint64_t* tfull_bar = empty_bar + kStages;
+    uint8_t* sf_smem = smem + kMxStages * kMxTileBytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(sf_smem + kMxStages * kMxSfBytes);
+    uint64_t* empty_bar = full_bar + kMxStages;
+    uint64_t* tfull_bar = empty_bar + kMxStages;
     uint64_t* tempty_bar = tfull_bar + 1;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* s_end = reinterpret_cast<int*>(sf_smem + kStages * kMxSfBytes + 256);
-    uint32_t* tr_smem = reinterpret_cast<uint32_t*>(sf_smem + kStages * kMxSfBytes + 256 + kMaxExperts * 4);
+    int* s_end = reinterpret_cast<int*>(sf_smem + kMxStages * kMxSfBytes + 256);
+    uint32_t* tr_smem = reinterpret_cast<uint32_t*>(sf_smem + kMxStages * kMxSfBytes + 256 + kMaxExperts * 4);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int E = p.tokens_per_expert ? p.num_experts : 1;
@@ -142,9 +149,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         for (int e = threadIdx.x; e < E; e += blockDim.x) s_end[e] = p.tokens_per_expert[e];
     }
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < kMxStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(tfull_bar, 1);
-        mbar_init(tempty_bar, 8);
+        mbar_init(tempty_bar, kMxEpiWarps);
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -240,7 +247,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                         bulk_load_1d(ssfb, sfb + so, 512, &full_bar[stage]);
                         bulk_load_1d(ssfb + 512, sfb + so + static_cast<size_t>(p.sfb_k_tiles) * 512, 512, &full_bar[stage]);
                     }
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if (++stage == kMxStages) { stage = 0; phase ^= 1; }
                 }
             }
         }
@@ -274,7 +281,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                                   tmem_base + kMxSfbCol, (kt > 0 || k > 0) ? 1u : 0u);
                     }
                     umma_commit(&empty_bar[stage]);
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if (++stage == kMxStages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
                 if (k_tiles > 0) umma_commit(tfull_bar);
@@ -283,10 +290,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps
-        // Eight warps: two per TMEM lane quarter (a warp may only read lanes 32*(warp%4)...), each
-        // taking half of the tile's columns, so a thread holds 128 accumulator columns as 64 packed words.
+        // Sixteen warps: four per TMEM lane quarter (a warp may only read lanes 32*(warp%4)...), each taking
+        // 64 of the tile's 256 columns, so a thread holds its share of the accumulator as 32 packed words and
+        // nothing spills.  More resident warps also hide the latency of the epilogue's loads and stores.
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int sub = (warp - 2) >> 2;                 // 0..3
         const int r_in_tile = quarter * 32 + lane;
         uint32_t* tr = tr_smem + (warp - 2) * kMxTrWords;
         int it = 0;
@@ -297,11 +305,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             if (!mbar_wait(tfull_bar, it & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-            uint32_t pk[64];
+            uint32_t pk[32];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                // GateUp: chunks {2h, 2h+1} of the gate half and the same two of the up half; else 4 consecutive chunks
-                const int col = (kEpi == kMxEpiGateUp) ? ((c >> 1) * (kBlockN / 2) + (half * 2 + (c & 1)) * 32) : (half * 4 + c) * 32;
+            for (int c = 0; c < 2; ++c) {
+                // GateUp: chunk `sub` of the gate half and chunk `sub` of the up half; otherwise two adjacent chunks
+                const int col = (kEpi == kMxEpiGateUp) ? (c * (kBlockN / 2) + sub * 32) : (sub * 2 + c) * 32;
                 uint32_t acc[32];
                 if (k_tiles > 0) { tmem_ld_32x32(t_addr + col, acc); tmem_ld_wait(); }
                 else {
@@ -319,10 +327,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             if constexpr (kEpi == kMxEpiStore) {
                 if (!(kWgrad && p.accumulate && k_tiles == 0)) {
                     __nv_bfloat16* dst = p.out_bf16 + (kWgrad ? static_cast<size_t>(expert) * p.out_expert_stride : 0) +
-                                         row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN + half * 128;
+                                         row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN + sub * 64;
                     uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-                    for (int v = 0; v < 16; ++v) {
+                    for (int v = 0; v < 8; ++v) {
                         uint32_t o[4] = {pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]};
                         if (kWgrad && p.accumulate) {
                             const uint4 old = d4[v];
@@ -337,46 +345,43 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     }
                 }
             } else if constexpr (kEpi == kMxEpiGateUp) {
+                const int col0 = n_idx * (kBlockN / 2) + sub * 32;
+                uint32_t g[16], u[16], h[16];
 #pragma unroll
-                for (int c = 0; c < 2; ++c) {
-                    const int col0 = n_idx * (kBlockN / 2) + (half * 2 + c) * 32;
-                    uint32_t g[16], u[16], h[16];
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        g[i] = pk[c * 16 + i];
-                        u[i] = pk[32 + c * 16 + i];
-                        float2 gf = unpack_bf16(g[i]), uf = unpack_bf16(u[i]);
-                        if (p.has_limit) {
-                            gf.x = fminf(gf.x, p.limit); gf.y = fminf(gf.y, p.limit);
-                            uf.x = fminf(fmaxf(uf.x, -p.limit), p.limit); uf.y = fminf(fmaxf(uf.y, -p.limit), p.limit);
-                        }
-                        h[i] = pack_bf16(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
+                for (int i = 0; i < 16; ++i) {
+                    g[i] = pk[i];
+                    u[i] = pk[16 + i];
+                    float2 gf = unpack_bf16(g[i]), uf = unpack_bf16(u[i]);
+                    if (p.has_limit) {
+                        gf.x = fminf(gf.x, p.limit); gf.y = fminf(gf.y, p.limit);
+                        uf.x = fminf(fmaxf(uf.x, -p.limit), p.limit); uf.y = fminf(fmaxf(uf.y, -p.limit), p.limit);
                     }
-                    mx_store_normal(g, p.q[0], p.sc[0], row, col0, p.q_cols);
-                    mx_store_normal(u, p.q[1], p.sc[1], row, col0, p.q_cols);
-                    mx_store_normal(h, p.q[2], p.sc[2], row, col0, p.q_cols);
-                    mx_store_transposed(h, tr, p.qt[2], p.sct[2], row, col0, p.t_rows, lane);
+                    h[i] = pack_bf16(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
                 }
+                mx_store_normal(g, p.q[0], p.sc[0], row, col0, p.q_cols);
+                mx_store_normal(u, p.q[1], p.sc[1], row, col0, p.q_cols);
+                mx_store_normal(h, p.q[2], p.sc[2], row, col0, p.q_cols);
+                mx_store_transposed(h, tr, p.qt[2], p.sct[2], row, col0, p.t_rows, lane);
             } else {
                 float inv_w = 0.0f;
                 if (p.row_scale) { const float w = p.row_scale[row]; inv_w = w > 0.0f ? 1.0f / w : 0.0f; }
                 float partial = 0.0f;
-                const int colbase = n_idx * kBlockN + half * 128;
+                const int colbase = n_idx * kBlockN + sub * 64;
                 uint4* dh4 = reinterpret_cast<uint4*>(p.out_bf16 + row * p.ld_out + colbase);
-                const size_t so0 = mx_scale_offset(static_cast<int>(row), colbase >> 5, p.q_cols >> 7);   // 4 consecutive bytes
-                const uint32_t gsc4 = *reinterpret_cast<const uint32_t*>(p.in_sc[0] + so0);
-                const uint32_t usc4 = *reinterpret_cast<const uint32_t*>(p.in_sc[1] + so0);
+                const size_t so0 = mx_scale_offset(static_cast<int>(row), colbase >> 5, p.q_cols >> 7);   // 2 consecutive bytes
+                const uint32_t gsc2 = *reinterpret_cast<const uint16_t*>(p.in_sc[0] + so0);
+                const uint32_t usc2 = *reinterpret_cast<const uint16_t*>(p.in_sc[1] + so0);
                 const uint4* gq = reinterpret_cast<const uint4*>(p.in_q[0] + row * p.q_cols + colbase);
                 const uint4* uq = reinterpret_cast<const uint4*>(p.in_q[1] + row * p.q_cols + colbase);
-                uint4 gnext0 = gq[0], gnext1 = gq[1], unext0 = uq[0], unext1 = uq[1];
+                uint4 gv[4], uv[4];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
+                for (int v = 0; v < 4; ++v) { gv[v] = gq[v]; uv[v] = uq[v]; }
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
                     const int col0 = colbase + c * 32;
-                    const uint4 g0 = gnext0, g1 = gnext1, u0 = unext0, u1 = unext1;
-                    if (c + 1 < 4) { gnext0 = gq[2 * c + 2]; gnext1 = gq[2 * c + 3]; unext0 = uq[2 * c + 2]; unext1 = uq[2 * c + 3]; }
-                    const float gs = mx_scale_value((gsc4 >> (8 * c)) & 0xFFu), us = mx_scale_value((usc4 >> (8 * c)) & 0xFFu);
-                    const uint32_t gb[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
-                    const uint32_t ub[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+                    const float gs = mx_scale_value((gsc2 >> (8 * c)) & 0xFFu), us = mx_scale_value((usc2 >> (8 * c)) & 0xFFu);
+                    const uint32_t gb[8] = {gv[2 * c].x, gv[2 * c].y, gv[2 * c].z, gv[2 * c].w, gv[2 * c + 1].x, gv[2 * c + 1].y, gv[2 * c + 1].z, gv[2 * c + 1].w};
+                    const uint32_t ub[8] = {uv[2 * c].x, uv[2 * c].y, uv[2 * c].z, uv[2 * c].w, uv[2 * c + 1].x, uv[2 * c + 1].y, uv[2 * c + 1].z, uv[2 * c + 1].w};
                     uint32_t dg[16], du[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
@@ -406,7 +411,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     mx_store_transposed(dg, tr, p.qt[0], p.sct[0], row, col0, p.t_rows, lane);
                     mx_store_transposed(du, tr, p.qt[1], p.sct[1], row, col0, p.t_rows, lane);
                 }
-                if (p.partials) p.partials[row * (2 * p.n_tiles) + 2 * n_idx + half] = partial;   // two column halves per tile
+                if (p.partials) p.partials[row * (4 * p.n_tiles) + 4 * n_idx + sub] = partial;   // four column slices per tile
             }
         }
     }

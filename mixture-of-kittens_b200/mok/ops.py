@@ -608,7 +608,7 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
         work_d_gate_qt=torch.empty(I, MB, **f8), work_d_gate_sct=torch.empty(_sc_shape(I, MB), **u8),
         work_d_up_qt=torch.empty(I, MB, **f8), work_d_up_sct=torch.empty(_sc_shape(I, MB), **u8),
         router_weights_routed=torch.empty(MB, dtype=torch.float32, device=dev),
-        d_router_weight_partials=torch.empty(MB, I // 128, dtype=torch.float32, device=dev))
+        d_router_weight_partials=torch.empty(MB, I // 64, dtype=torch.float32, device=dev))
 
     a = _lib.BwdMxfp8Args()
     a.c = _common(x, ep_size, I, El, topk, cap, MB, minibatch_size, num_comm_sms, swiglu_limit,
