@@ -240,7 +240,7 @@ int mok_profile_collect(double* ms_per_slot, long long* launches_per_slot);
  * tcgen05.  a_mn_major / b_mn_major select the memory layout of the operands:
  *   A: 0 = [M, K] row-major (K-major), 1 = [K, M] row-major (M-major)
  *   B: 0 = [N, K] row-major (K-major), 1 = [K, N] row-major (N-major)
- * M % 128 == 0, N % 256 == 0, K % 64 == 0. */
+ * M % 256 == 0, N % 256 == 0, K % 64 == 0. */
 int mok_gemm_bf16(const void* a, const void* b, void* c, int m, int n, int k,
                   int a_mn_major, int b_mn_major, int32_t* status, void* stream);
 

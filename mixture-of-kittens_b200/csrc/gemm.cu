@@ -2,6 +2,7 @@
 // plain-GEMM entry point used by the tests.
 #include "gemm.cuh"
 
+#include <cstdlib>
 #include <mutex>
 
 namespace mok {
@@ -52,10 +53,10 @@ int device_sm_count() {
 }
 
 namespace {
-template <int kA, int kB, int kEpi, bool kW>
+template <int kA, int kB, int kEpi, bool kW, bool k2>
 int launch_inst(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap& a1, const CUtensorMap& b1, const GemmParams& p,
                 int grid, cudaStream_t stream) {
-    auto* kern = grouped_gemm_kernel<kA, kB, kEpi, kW>;
+    auto* kern = grouped_gemm_kernel<kA, kB, kEpi, kW, k2>;
     static bool configured[64] = {false};   // per instantiation and device: the attribute is sticky
     int dev = 0;
     MOK_CUDA_CHECK(cudaGetDevice(&dev));
@@ -63,9 +64,29 @@ int launch_inst(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap&
         MOK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmemBytes));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }
-    kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(a0, b0, a1, b1, p);
+    if (k2) {      // pairs of CTAs on neighbouring SMs: cluster of 2
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(grid & ~1);
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = kGemmSmemBytes;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr{};
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        MOK_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, a0, b0, a1, b1, p));
+    } else {
+        kern<<<grid, kGemmThreads, kGemmSmemBytes, stream>>>(a0, b0, a1, b1, p);
+    }
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
+}
+
+// two-CTA tiles (256 rows per CTA pair) unless MOK_B200_2CTA=0
+bool use_pairs() {
+    static const bool on = [] { const char* e = std::getenv("MOK_B200_2CTA"); return !(e && e[0] == '0'); }();
+    return on;
 }
 }  // namespace
 
@@ -76,7 +97,9 @@ int launch_grouped_gemm(int a_major, int b_major, int epi, bool wgrad, const Gem
     // A: K-major box {64 K, 128 rows}; M-major box {64 M, 64 K-rows}
     const uint32_t a_box_outer = a_major == kMajorK ? kBlockM : kBlockK;
     // B: K-major box {64 K, 256 rows} (128 when the tile is split into gate|up halves); N-major box {64 N, 64 K-rows}
-    const uint32_t b_box_outer = b_major == kMajorK ? (epi == kEpiSwigluFwd ? kBlockN / 2 : kBlockN) : kBlockK;
+    const bool pairs = use_pairs();
+    // (a CTA of a pair stages 128 rows of B, so its box is 128 rows too)
+    const uint32_t b_box_outer = b_major == kMajorK ? ((epi == kEpiSwigluFwd || pairs) ? kBlockN / 2 : kBlockN) : kBlockK;
     int rc;
     if ((rc = make_tmap_2d(&a0, ops.a0, ops.a_inner, ops.a_outer, ops.a_inner * 2, 64, a_box_outer, 2))) return rc;
     if ((rc = make_tmap_2d(&b0, ops.b0, ops.b_inner, ops.b_outer, ops.b_inner * 2, 64, b_box_outer, 2))) return rc;
@@ -84,19 +107,24 @@ int launch_grouped_gemm(int a_major, int b_major, int epi, bool wgrad, const Gem
     if ((rc = make_tmap_2d(&b1, ops.b1 ? ops.b1 : ops.b0, ops.b_inner, ops.b_outer, ops.b_inner * 2, 64, b_box_outer, 2))) return rc;
     int ctas = device_sm_count();
     if (max_ctas > 0 && max_ctas < ctas) ctas = max_ctas;
-    const int grid = max_tiles < ctas ? max_tiles : ctas;
+    // max_tiles counts 128-row tiles; a pair covers two of them
+    const int want = pairs ? ((max_tiles + 1) / 2) * 2 : max_tiles;
+    const int grid = want < ctas ? want : (pairs ? (ctas & ~1) : ctas);
     ProfScope prof(prof_slot, stream);
+#define MOK_INST(A, B, EPI, W)                                                              \
+    (pairs ? launch_inst<A, B, EPI, W, true>(a0, b0, a1, b1, p, grid, stream)              \
+           : launch_inst<A, B, EPI, W, false>(a0, b0, a1, b1, p, grid, stream))
 
     if (!wgrad && a_major == kMajorK && b_major == kMajorK && epi == kEpiStore)
-        return launch_inst<kMajorK, kMajorK, kEpiStore, false>(a0, b0, a1, b1, p, grid, stream);
+        return MOK_INST(kMajorK, kMajorK, kEpiStore, false);
     if (!wgrad && a_major == kMajorK && b_major == kMajorK && epi == kEpiSwigluFwd)
-        return launch_inst<kMajorK, kMajorK, kEpiSwigluFwd, false>(a0, b0, a1, b1, p, grid, stream);
+        return MOK_INST(kMajorK, kMajorK, kEpiSwigluFwd, false);
     if (!wgrad && a_major == kMajorK && b_major == kMajorMN && epi == kEpiStore)
-        return launch_inst<kMajorK, kMajorMN, kEpiStore, false>(a0, b0, a1, b1, p, grid, stream);
+        return MOK_INST(kMajorK, kMajorMN, kEpiStore, false);
     if (!wgrad && a_major == kMajorK && b_major == kMajorMN && epi == kEpiSwigluBwd)
-        return launch_inst<kMajorK, kMajorMN, kEpiSwigluBwd, false>(a0, b0, a1, b1, p, grid, stream);
+        return MOK_INST(kMajorK, kMajorMN, kEpiSwigluBwd, false);
     if (wgrad && a_major == kMajorMN && b_major == kMajorMN && epi == kEpiStore)
-        return launch_inst<kMajorMN, kMajorMN, kEpiStore, true>(a0, b0, a1, b1, p, grid, stream);
+        return MOK_INST(kMajorMN, kMajorMN, kEpiStore, true);
     return MOK_ERR_UNSUPPORTED;
 }
 
@@ -106,7 +134,7 @@ extern "C" int mok_gemm_bf16(const void* a, const void* b, void* c, int m, int n
                              int32_t* status, void* stream) {
     using namespace mok;
     if (!a || !b || !c || m <= 0 || n <= 0 || k <= 0) return MOK_ERR_INVALID;
-    if (m % kBlockM || n % kBlockN || k % kBlockK) return MOK_ERR_INVALID;
+    if (m % (2 * kBlockM) || n % kBlockN || k % kBlockK) return MOK_ERR_INVALID;
     GemmParams p{};
     p.num_tokens = nullptr;
     p.capacity = 0;

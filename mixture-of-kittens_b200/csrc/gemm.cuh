@@ -36,7 +36,7 @@ constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kGemmThreads = 192;
 constexpr int kTmemCols = 512;
 constexpr int kMaxExperts = MOK_MAX_LOCAL_EXPERTS;
-constexpr int kGemmSmemBytes = kStages * kStageBytes + 256 + kMaxExperts * 4 + 1024;
+constexpr int kGemmSmemBytes = kStages * kStageBytes + 256 + kMaxExperts * 4 + 1024;   // also 6 x 32 KB stages of the two-CTA form
 
 struct GemmParams {
     // row domain
@@ -81,20 +81,30 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
     return g * sigmoid_fast(g) * u;
 }
 
-template <int kAMajor, int kBMajor, int kEpi, bool kWgrad>
+template <int kAMajor, int kBMajor, int kEpi, bool kWgrad, bool k2>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                     const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
                     const GemmParams p) {
+    // k2: a pair of CTAs (cluster of 2) shares one 256 x 256 tile; each CTA stages its own 128 rows of A and
+    // its own 128 rows/columns of B, so a stage is 32 KB and six stages fit
+    constexpr int kS = k2 ? 6 : kStages;
+    constexpr int kBTile = k2 ? kBBytes / 2 : kBBytes;
+    constexpr int kStg = kABytes + kBTile;
+    constexpr int kTileM = k2 ? 2 * kBlockM : kBlockM;
+    const uint32_t cta_rank = k2 ? cluster_cta_rank() : 0u;
+    const bool leader = cta_rank == 0;
+    const int tile_first = k2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int tile_step = k2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-    uint64_t* empty_bar = full_bar + kStages;
-    uint64_t* tfull_bar = empty_bar + kStages;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kS * kStg);
+    uint64_t* empty_bar = full_bar + kS;
+    uint64_t* tfull_bar = empty_bar + kS;
     uint64_t* tempty_bar = tfull_bar + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    int* s_end = reinterpret_cast<int*>(smem + kStages * kStageBytes + 256);
+    int* s_end = reinterpret_cast<int*>(smem + kS * kStg + 256);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int E = p.tokens_per_expert ? p.num_experts : 1;
@@ -104,8 +114,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         for (int e = threadIdx.x; e < E; e += blockDim.x) s_end[e] = p.tokens_per_expert[e];
     }
     if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], 4); }
+        for (int s = 0; s < kS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], k2 ? 8 : 4); }
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -120,9 +130,13 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         int run = incl - sum;
         for (int j = 0; j < per; ++j) { const int e = lane * per + j; if (e < E) { run += s_end[e]; s_end[e] = run; } }
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+    if (warp == 1) {
+        if (k2) { tmem_alloc_pair(tmem_slot, kTmemCols); tmem_relinquish_pair(); }
+        else { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+    }
     tc_fence_before();
     __syncthreads();
+    if (k2) cluster_sync_all();        // the partner's barriers are initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -131,14 +145,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     // a weight-gradient launch that only accumulates has nothing to do on an empty window
     int chunk_lo = 0, chunk_hi = win_rows;
     if (!kWgrad) chunk_range(win_rows, p.chunk, chunk_lo, chunk_hi);
-    const int m_tile0 = chunk_lo / kBlockM;
-    const int num_tiles = kWgrad ? ((p.accumulate && win_rows == 0) ? 0 : E * p.m_tiles_w * p.n_tiles)
-                                 : ((chunk_hi - chunk_lo) / kBlockM) * p.n_tiles;
+    const int m_tile0 = chunk_lo / kTileM;
+    const int m_tiles_w = k2 ? p.m_tiles_w >> 1 : p.m_tiles_w;
+    const int num_tiles = kWgrad ? ((p.accumulate && win_rows == 0) ? 0 : E * m_tiles_w * p.n_tiles)
+                                 : ((chunk_hi - chunk_lo) / kTileM) * p.n_tiles;
 
     // tile -> coordinates.  a_row: first A/C row (window-relative); k_row0/k_blocks: contraction range
     auto decode = [&](int tile, int& m_idx, int& n_idx, int& expert, int& k_row0, int& k_blocks) {
         if constexpr (kWgrad) {
-            const int per_e = p.m_tiles_w * p.n_tiles;
+            const int per_e = m_tiles_w * p.n_tiles;
             expert = tile / per_e;
             const int r = tile - expert * per_e;
             m_idx = r / p.n_tiles;
@@ -154,7 +169,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             m_idx = m_tile0 + m_rel;
             expert = 0;
             if (p.tokens_per_expert) {
-                const int g = p.row_offset + m_idx * kBlockM;
+                const int g = p.row_offset + m_idx * kTileM;
                 int lo = 0, hi = E - 1;
                 while (lo < hi) { const int mid = (lo + hi) >> 1; if (s_end[mid] > g) hi = mid; else lo = mid + 1; }
                 expert = lo;
@@ -172,49 +187,59 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             if (p.num_segs > 1 || kEpi == kEpiSwigluFwd) { tma_prefetch_desc(&tmB1); }
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step) {
                 int m_idx, n_idx, expert, k_row0, k_blocks;
                 decode(tile, m_idx, n_idx, expert, k_row0, k_blocks);
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
-                    uint8_t* sa = smem + stage * kStageBytes;
+                    uint8_t* sa = smem + stage * kStg;
                     uint8_t* sb = sa + kABytes;
-                    mbar_arrive_expect_tx(&full_bar[stage], kStageBytes);
+                    if (leader) mbar_arrive_expect_tx(&full_bar[stage], k2 ? 2 * kStg : kStg);
+                    const int row_a = m_idx * kTileM + static_cast<int>(cta_rank) * kBlockM;   // this CTA's 128 rows / columns of A
+                    const int col_b = n_idx * kBlockN + static_cast<int>(cta_rank) * (kBlockN / 2);
+                    auto load = [&](void* dst, const CUtensorMap* map, int x, int y) {
+                        if (k2) tma_load_2d_pair(dst, map, &full_bar[stage], x, y);
+                        else tma_load_2d(dst, map, &full_bar[stage], x, y);
+                    };
                     const int seg = (!kWgrad && kb >= p.k_blocks_per_seg) ? 1 : 0;
                     const int kk = (kWgrad ? kb : kb - seg * p.k_blocks_per_seg) * kBlockK;
                     const CUtensorMap* ma = seg ? &tmA1 : &tmA0;
                     const CUtensorMap* mb = seg ? &tmB1 : &tmB0;
                     // A
                     if constexpr (kAMajor == kMajorK) {
-                        tma_load_2d(sa, ma, &full_bar[stage], kk, m_idx * kBlockM);
+                        load(sa, ma, kk, row_a);
                     } else {
 #pragma unroll
                         for (int j = 0; j < kBlockM / 64; ++j)
-                            tma_load_2d(sa + j * (kBlockK * 128), ma, &full_bar[stage], m_idx * kBlockM + j * 64, k_row0 + kk);
+                            load(sa + j * (kBlockK * 128), ma, row_a + j * 64, k_row0 + kk);
                     }
                     // B
                     if constexpr (kBMajor == kMajorK) {
                         if constexpr (kEpi == kEpiSwigluFwd) {
                             const int y = expert * p.b_rows_per_expert + n_idx * (kBlockN / 2);
-                            tma_load_2d(sb, &tmB0, &full_bar[stage], kk, y);
-                            tma_load_2d(sb + kBBytes / 2, &tmB1, &full_bar[stage], kk, y);
+                            if (k2) {                       // the leader holds the gate rows, its partner the up rows
+                                load(sb, leader ? &tmB0 : &tmB1, kk, y);
+                            } else {
+                                load(sb, &tmB0, kk, y);
+                                load(sb + kBBytes / 2, &tmB1, kk, y);
+                            }
                         } else {
-                            tma_load_2d(sb, mb, &full_bar[stage], kk, expert * p.b_rows_per_expert + n_idx * kBlockN);
+                            load(sb, mb, kk, expert * p.b_rows_per_expert + (k2 ? col_b : n_idx * kBlockN));
                         }
                     } else {
                         const int y = kWgrad ? (k_row0 + kk) : (expert * p.b_rows_per_expert + kk);
 #pragma unroll
-                        for (int j = 0; j < kBlockN / 64; ++j)
-                            tma_load_2d(sb + j * (kBlockK * 128), mb, &full_bar[stage], n_idx * kBlockN + j * 64, y);
+                        for (int j = 0; j < (k2 ? kBlockN / 128 : kBlockN / 64); ++j)
+                            load(sb + j * (kBlockK * 128), mb, (k2 ? col_b : n_idx * kBlockN) + j * 64, y);
                     }
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if (++stage == kS) { stage = 0; phase ^= 1; }
                 }
             }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_bf16(kBlockM, kBlockN, kAMajor, kBMajor);
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = make_idesc_bf16(kTileM, kBlockN, kAMajor, kBMajor);
             constexpr uint32_t a_lbo = kAMajor == kMajorK ? 16 : kBlockK * 128;
             constexpr uint32_t b_lbo = kBMajor == kMajorK ? 16 : kBlockK * 128;
             constexpr uint32_t a_kstep = kAMajor == kMajorK ? 32 : 2048;   // bytes per K=16 step
@@ -222,7 +247,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++it) {
                 int m_idx, n_idx, expert, k_row0, k_blocks;
                 decode(tile, m_idx, n_idx, expert, k_row0, k_blocks);
                 const int buf = it & 1;
@@ -233,21 +258,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + stage * kStageBytes);
+                    const uint32_t sa = smem_u32(smem + stage * kStg);
                     const uint32_t sb = sa + kABytes;
                     const uint64_t adesc = make_smem_desc(sa, a_lbo, 1024);
                     const uint64_t bdesc = make_smem_desc(sb, b_lbo, 1024);
 #pragma unroll
                     for (int k = 0; k < kBlockK / 16; ++k) {
-                        umma_f16(d_tmem, adesc + ((k * a_kstep) >> 4), bdesc + ((k * b_kstep) >> 4), idesc,
-                                 (kb > 0 || k > 0) ? 1u : 0u);
+                        if (k2) umma_f16_pair(d_tmem, adesc + ((k * a_kstep) >> 4), bdesc + ((k * b_kstep) >> 4), idesc,
+                                              (kb > 0 || k > 0) ? 1u : 0u);
+                        else umma_f16(d_tmem, adesc + ((k * a_kstep) >> 4), bdesc + ((k * b_kstep) >> 4), idesc,
+                                      (kb > 0 || k > 0) ? 1u : 0u);
                     }
-                    umma_commit(&empty_bar[stage]);
-                    if (++stage == kStages) { stage = 0; phase ^= 1; }
+                    if (k2) umma_commit_pair(&empty_bar[stage]); else umma_commit(&empty_bar[stage]);
+                    if (++stage == kS) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                if (k_blocks > 0) umma_commit(&tfull_bar[buf]);
-                else mbar_arrive(&tfull_bar[buf]);
+                if (k_blocks > 0) { if (k2) umma_commit_pair(&tfull_bar[buf]); else umma_commit(&tfull_bar[buf]); }
+                else { mbar_arrive(&tfull_bar[buf]); if (k2) mbar_arrive_cta(&tfull_bar[buf], 1); }
             }
         }
     } else {
@@ -256,7 +283,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
         const int r_in_tile = quarter * 32 + lane;
         int it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++it) {
             int m_idx, n_idx, expert, k_row0, k_blocks;
             decode(tile, m_idx, n_idx, expert, k_row0, k_blocks);
             const int buf = it & 1;
@@ -264,7 +291,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             if (!mbar_wait(&tfull_bar[buf], acc_phase, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * kBlockN;
-            const size_t row = static_cast<size_t>(m_idx) * kBlockM + r_in_tile;
+            const size_t row = static_cast<size_t>(m_idx) * kTileM + cta_rank * kBlockM + r_in_tile;
 
             if constexpr (kEpi == kEpiStore) {
                 __nv_bfloat16* dst = p.out0 + (kWgrad ? static_cast<size_t>(expert) * p.out_expert_stride : 0) +
@@ -375,14 +402,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+            if (lane == 0) { if (k2) mbar_arrive_leader(&tempty_bar[buf]); else mbar_arrive(&tempty_bar[buf]); }
         }
     }
 
     // ---------------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+    if (k2) cluster_sync_all();        // neither CTA frees tensor memory or exits while its partner may still signal it
+    if (warp == 1) { tc_fence_after(); if (k2) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols); }
     if (threadIdx.x == 0 && *abort_flag) report_status(p.status, MOK_STATUS_PIPELINE_TIMEOUT, warp);
 }
 

@@ -165,7 +165,7 @@ def test_epilogue_constants_and_many_tokens(cuda_device):
 # tcgen05 GEMM building block, all operand layouts
 # ----------------------------------------------------------------------------------------
 @pytest.mark.parametrize("a_mn,b_mn", [(0, 0), (0, 1), (1, 1)])
-@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (256, 512, 256), (1024, 768, 2048), (384, 256, 4160)])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (256, 512, 256), (1024, 768, 2048), (768, 256, 4160)])
 def test_gemm_bf16_layouts(cuda_device, a_mn, b_mn, m, n, k):
     mok = _mok()
     L = mok._lib
