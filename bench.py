@@ -53,6 +53,14 @@ WORKLOADS = {
     "C4": dict(T=16384, H=7168, I=2048, E=256, K=8, router="linear", backward=True, mxfp8=True,
                minibatch=4096, macrobatch=131072, multiplier=0.5,
                desc="MXFP8 fwd+bwd, 16384 tokens/rank, H=7168, 256 experts, top-8, I=2048"),
+    # skewed-routing stress (BASELINE config 5): C4 shapes, expert popularity ~ Zipf(1.2) with the popular
+    # experts dealt round-robin to the ranks, schedule_capacity_multiplier 1.0
+    "C5": dict(T=16384, H=7168, I=2048, E=256, K=8, router="linear", backward=True, mxfp8=True, zipf=1.2,
+               minibatch=4096, macrobatch=131072, multiplier=1.0,
+               desc="MXFP8 fwd+bwd, C4 shapes, Zipf(1.2) expert popularity, capacity multiplier 1.0"),
+    "C5-bf16": dict(T=16384, H=7168, I=2048, E=256, K=8, router="linear", backward=True, zipf=1.2,
+                    minibatch=4096, macrobatch=131072, multiplier=1.0,
+                    desc="BF16 fwd+bwd, C4 shapes, Zipf(1.2) expert popularity, capacity multiplier 1.0"),
     "C4x1": dict(T=16384, H=7168, I=2048, E=32, K=8, router="linear", backward=True, mxfp8=True,
                  minibatch=4096, macrobatch=131072, multiplier=0.5,
                  desc="MXFP8 fwd+bwd, one GPU's share of C4: 16384 tokens, H=7168, 32 local experts, top-8, I=2048"),
@@ -62,7 +70,9 @@ WORKLOADS = {
 }
 # DRAM bytes per launch of the dominant kernel from the ncu capture summarised under profiles/
 # (filled in per workload once captured; None = not captured)
-NCU_TRAFFIC_BYTES = {"C2": None, "C3": None}
+# C2: routed gate|up GEMM captured at 2048 tokens (946 MB read + 133 MB written, of which 805 MB are the weights,
+# read once whatever the row count) and scaled by rows to the full launch: 0.805e9 + 147456 rows * 8362 B
+NCU_TRAFFIC_BYTES = {"C2": 2.04e9, "C3": None}
 
 
 def layer_flops(T, K, H, I, backward):
@@ -137,6 +147,11 @@ def make_inputs(wl, rank, world, dev):
         logits = x.float() @ w_r.T
     else:
         logits = torch.rand(T, E, generator=g, device=dev)
+    if wl.get("zipf"):
+        e = torch.arange(E, device=dev)
+        zipf_rank = (e % El) * world + (e // El) + 1          # popular experts dealt round-robin to the ranks
+        p = zipf_rank.float() ** (-wl["zipf"])
+        logits = logits + torch.log(p / p.sum())
     vals, idx = torch.topk(torch.softmax(logits, dim=-1), K, dim=-1)
     rw = (vals / vals.sum(-1, keepdim=True)).float()
     d_out = torch.randn(T, H, generator=g, device=dev).to(torch.bfloat16)
@@ -171,6 +186,11 @@ def run_ours(args, rank, world, local_rank):
     ws = F.get_workspace(cfg, dist.group.WORLD, device=dev, num_local_tokens=T, hidden_size=H, topk=K)
     host, params = make_inputs(wl, rank, world, dev)
     dev_in = {k: v.to(dev) for k, v in host.items()}
+    # share of all routes that lands on the busiest rank (1/world when balanced)
+    dest = torch.bincount((dev_in["topk"] // El).flatten(), minlength=world).double()
+    if world > 1:
+        dist.all_reduce(dest)
+    max_rank_share = (dest.max() / dest.sum()).item()
     out_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
     dx_host = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
     drw_host = torch.empty(T, K, dtype=torch.float32).pin_memory()
@@ -302,7 +322,8 @@ def run_ours(args, rank, world, local_rank):
         "dtype": "mxfp8 (e4m3 x e8m0, fp32 accumulate)" if wl.get("mxfp8") else "bf16", "data": "synthetic",
         "config": {"workload": f"{name}: {wl['desc']}", "ep_size": world, "tokens_per_rank": T, "hidden": H,
                    "intermediate": I, "experts": E, "topk": K, "minibatch_size": wl["minibatch"],
-                   "macrobatch_size": wl["macrobatch"], "pass": "fwd+bwd" if wl["backward"] else "fwd (incl. build_schedule)",
+                   "macrobatch_size": wl["macrobatch"], "capacity_multiplier": wl["multiplier"],
+                   "busiest_rank_share_of_routes": max_rank_share, "pass": "fwd+bwd" if wl["backward"] else "fwd (incl. build_schedule)",
                    "l2": "inputs larger than L2 (no flush needed)", "per_gpu_tflops": flops / (ms_step * 1e-3) / 1e12,
                    "pct_of_measured_bf16_peak": 100.0 * flops / (ms_step * 1e-3) / 1e12 / peaks["tflops"]},
         "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
