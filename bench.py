@@ -287,14 +287,39 @@ def run_ours(args, rank, world, local_rank):
         step(dev_in)
     torch.cuda.synchronize()
     mok.raise_for_status(dev)
-    L.mok_profile_enable(1)
-    L.profile_collect()
     launches0 = L.mok_launch_count()
     ms_step = timed(lambda: step(dev_in), args.steps)
     launches = L.mok_launch_count() - launches0
+    # the same K steps again with a CUDA-event pair around every launch: the per-kernel split behind `roofline`
+    # (the event records cost a little, so `value` comes from the region above)
+    L.mok_profile_enable(1)
+    L.profile_collect()
+    ms_step_events = timed(lambda: step(dev_in), args.steps)
     prof = L.profile_collect()
     L.mok_profile_enable(0)
+    ms_graph = None
+    if args.graph and world == 1:        # the same step captured once and replayed as a CUDA graph
+        side = torch.cuda.Stream(dev)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            step(dev_in)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            graph_out = step(dev_in)
+        graph.replay()
+        torch.cuda.synchronize()
+        eager_out = step(dev_in)
+        assert torch.equal(graph_out[0], eager_out[0]), "graph replay differs from the eager step"
+        ms_graph = timed(graph.replay, args.steps)
     clocks = sampler.stop() if rank == 0 else None
+    # rows this rank's schedule holds against the routes it received (expert groups are padded to 256 rows)
+    sched0 = F.build_schedule(ws, cfg, dev_in["topk"], num_local_experts=El)
+    n_rows = int(sched0.num_tokens.item())
+    n_routes = int((sched0.peer_rank[:min(n_rows, sched0.peer_rank.numel())] >= 0).sum().item())
+    out_a, _ = step(dev_in)
+    out_b, _ = step(dev_in)
+    rerun_identical = bool(torch.equal(out_a, out_b))
 
     for _ in range(3):
         step_e2e()
@@ -324,6 +349,10 @@ def run_ours(args, rank, world, local_rank):
                    "intermediate": I, "experts": E, "topk": K, "minibatch_size": wl["minibatch"],
                    "macrobatch_size": wl["macrobatch"], "capacity_multiplier": wl["multiplier"],
                    "busiest_rank_share_of_routes": max_rank_share, "pass": "fwd+bwd" if wl["backward"] else "fwd (incl. build_schedule)",
+                   "rank0_schedule_rows": n_rows, "rank0_routes": n_routes,
+                   "padding_overhead": (n_rows / n_routes - 1.0) if n_routes else None,
+                   "rerun_bit_identical": rerun_identical,
+                   "ms_per_step_with_kernel_events": ms_step_events,
                    "l2": "inputs larger than L2 (no flush needed)", "per_gpu_tflops": flops / (ms_step * 1e-3) / 1e12,
                    "pct_of_measured_bf16_peak": 100.0 * flops / (ms_step * 1e-3) / 1e12 / peaks["tflops"]},
         "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
@@ -337,6 +366,9 @@ def run_ours(args, rank, world, local_rank):
                      "ms_per_step": dom_ms_step},
         "kernel_ms_per_step": {k: v[0] / args.steps for k, v in sorted(prof.items())},
     }
+    if ms_graph is not None:
+        line["cuda_graph"] = {"ms_per_step": ms_graph, "value": flops / (ms_graph * 1e-3) / 1e12, "unit": UNIT,
+                              "note": "the same step captured once with torch.cuda.graph and replayed"}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(name, steps=1)
     print(json.dumps(line), flush=True)
@@ -394,6 +426,7 @@ def main():
     ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per rank (profiling a reduced case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--graph", action="store_true", help="also time the step replayed as one CUDA graph (1 GPU)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

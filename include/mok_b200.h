@@ -99,6 +99,26 @@ int mok_fwd_epilogue(const void* y_shared, const void* combine_buffer, const flo
 int mok_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* d_x,
                      int num_local_tokens, int hidden, int topk, void* stream);
 
+/* Single-rank epilogues that gather the routed rows through the schedule instead of reading a combine buffer:
+ *   out[t] = bf16(y_shared[t] + sum_k w[t,k] * y_routed[row(t,k)])            (forward)
+ *   d_x[t] = bf16(d_x_shared[t] + sum_k d_x_routed[row(t,k)]),
+ *   d_router_weights[t,k] = sum over columns of partials[row(t,k), :]          (backward)
+ * where row(t,k) is the schedule row whose peer_token_idx is t*K+k, the same fp32 sums in the same k order as
+ * mok_fwd_epilogue / mok_bwd_epilogue after a combine, so results are bit-identical to the two-step path.  They
+ * follow a layer call made with defer_combine = 1 and save the combine pass over [T*K, hidden] (one write and
+ * one read of it).  `route_row` is caller-provided scratch of T*K int32.  A route without a row (capacity
+ * overflow, flagged in the status word by the scheduler) contributes zero.
+ * No reference counterpart: the reference always combines into the symmetric buffer and then runs
+ * fwd_epilogue / bwd_epilogue (mok/functional.py:569-571, 698-700). */
+int mok_fwd_epilogue_rows(const void* y_shared, const void* y_routed, const int32_t* schedule_peer_rank,
+                          const int32_t* schedule_peer_token_idx, const int32_t* num_tokens,
+                          const float* topk_weights, int32_t* route_row, void* output, int num_local_tokens,
+                          int hidden, int topk, int row_limit, void* stream);
+int mok_bwd_epilogue_rows(const void* d_x_shared, const void* d_x_routed, const float* partials, int partial_cols,
+                          const int32_t* schedule_peer_rank, const int32_t* schedule_peer_token_idx,
+                          const int32_t* num_tokens, int32_t* route_row, void* d_x, float* d_router_weights,
+                          int num_local_tokens, int hidden, int topk, int row_limit, void* stream);
+
 /* ---- the fused layer passes -------------------------------------------------------------
  * All tensors are row-major and contiguous.  T = num_local_tokens, H = hidden, I = intermediate,
  * El = num_local_experts, K = topk, MB = macrobatch_size, cap = schedule_capacity.  Pointer
@@ -110,6 +130,10 @@ typedef struct mok_layer_common {
     int schedule_capacity, macrobatch_size, minibatch_size, num_comm_sms;
     int has_swiglu_limit;
     float swiglu_limit;
+    int defer_combine;                      /* 1: leave the routed results in their rows (y_routed, or d_x_routed and the
+                                               router-gradient partials) for mok_*_epilogue_rows instead of moving them
+                                               to the combine buffers; accepted only with ep_size 1 and
+                                               schedule_capacity <= macrobatch_size, else MOK_ERR_INVALID */
     const int32_t* schedule_peer_rank;      /* [cap] */
     const int32_t* schedule_peer_token_idx; /* [cap] */
     const int32_t* num_tokens;              /* [1]   */

@@ -98,6 +98,71 @@ __global__ void __launch_bounds__(256) epilogue_kernel(const uint4* __restrict__
     }
 }
 
+// route -> schedule row, for the epilogues that gather routed rows straight from the GEMM output
+__global__ void __launch_bounds__(256) invert_rows_kernel(const int* __restrict__ peer_rank, const int* __restrict__ peer_token_idx,
+                                                          const int* __restrict__ num_tokens, int row_limit, int routes,
+                                                          int* __restrict__ route_row) {
+    const int n = min(*num_tokens, row_limit);
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+        if (peer_rank[i] < 0) continue;
+        const int r = peer_token_idx[i];
+        if (r >= 0 && r < routes) route_row[r] = i;
+    }
+}
+
+// same arithmetic as epilogue_kernel, but the k-th routed row of token t is rows[route_row[t*K+k]]
+// (a route without a row adds nothing); kWeighted = forward, else backward, which also sums each
+// route's router-gradient partials in column order
+template <bool kWeighted>
+__global__ void __launch_bounds__(256) epilogue_rows_kernel(const uint4* __restrict__ shared_rows, const uint4* __restrict__ rows,
+                                                            const int* __restrict__ route_row, const float* __restrict__ weights,
+                                                            const float* __restrict__ partials, int partial_cols,
+                                                            float* __restrict__ d_router_weights, uint4* __restrict__ out,
+                                                            int64_t T, int vec_per_row, int K) {
+    const int64_t total = T * vec_per_row;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int64_t t = i / vec_per_row;
+        const int v = static_cast<int>(i - t * vec_per_row);
+        const uint4 s = shared_rows[i];
+        float acc[8];
+        {
+            const uint32_t w[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = unpack_bf16(w[j]);
+                acc[2 * j] = f.x; acc[2 * j + 1] = f.y;
+            }
+        }
+        for (int k = 0; k < K; ++k) {
+            const int row = route_row[t * K + k];
+            if (!kWeighted && v == 0) {
+                float sum = 0.0f;
+                if (row >= 0)
+                    for (int c = 0; c < partial_cols; ++c) sum += partials[static_cast<size_t>(row) * partial_cols + c];
+                d_router_weights[t * K + k] = sum;
+            }
+            if (row < 0) continue;
+            const uint4 q = rows[static_cast<int64_t>(row) * vec_per_row + v];
+            const float wk = kWeighted ? weights[t * K + k] : 1.0f;
+            const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 f = unpack_bf16(w[j]);
+                if (kWeighted) {
+                    acc[2 * j] += __fmul_rn(f.x, wk);
+                    acc[2 * j + 1] += __fmul_rn(f.y, wk);
+                } else {
+                    acc[2 * j] += f.x;
+                    acc[2 * j + 1] += f.y;
+                }
+            }
+        }
+        out[i] = make_uint4(pack_bf16(acc[0], acc[1]), pack_bf16(acc[2], acc[3]), pack_bf16(acc[4], acc[5]),
+                            pack_bf16(acc[6], acc[7]));
+    }
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------
@@ -444,6 +509,58 @@ extern "C" int mok_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_b
     epilogue_kernel<false><<<epilogue_grid(static_cast<int64_t>(num_local_tokens) * vpr), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         static_cast<const uint4*>(d_x_shared), static_cast<const uint4*>(d_x_routed_buffer), nullptr,
         static_cast<uint4*>(d_x), num_local_tokens, vpr, topk);
+    MOK_CUDA_CHECK(cudaGetLastError());
+    return MOK_OK;
+}
+
+namespace {
+int invert_rows(const int32_t* peer_rank, const int32_t* peer_token_idx, const int32_t* num_tokens, int32_t* route_row,
+                int routes, int row_limit, cudaStream_t s) {
+    MOK_CUDA_CHECK(cudaMemsetAsync(route_row, 0xFF, static_cast<size_t>(routes) * sizeof(int32_t), s));
+    mok::invert_rows_kernel<<<std::min(1024, (row_limit + 255) / 256), 256, 0, s>>>(peer_rank, peer_token_idx, num_tokens, row_limit,
+                                                                                    routes, route_row);
+    MOK_CUDA_CHECK(cudaGetLastError());
+    return MOK_OK;
+}
+}  // namespace
+
+extern "C" int mok_fwd_epilogue_rows(const void* y_shared, const void* y_routed, const int32_t* schedule_peer_rank,
+                                     const int32_t* schedule_peer_token_idx, const int32_t* num_tokens,
+                                     const float* topk_weights, int32_t* route_row, void* output, int num_local_tokens,
+                                     int hidden, int topk, int row_limit, void* stream) {
+    if (!y_shared || !y_routed || !schedule_peer_rank || !schedule_peer_token_idx || !num_tokens || !topk_weights ||
+        !route_row || !output)
+        return MOK_ERR_INVALID;
+    if (num_local_tokens <= 0 || hidden <= 0 || hidden % 8 || topk <= 0 || row_limit <= 0) return MOK_ERR_INVALID;
+    if (static_cast<int64_t>(num_local_tokens) * topk > INT32_MAX) return MOK_ERR_TOO_LARGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int vpr = hidden / 8;
+    ProfScope prof(kSlotEpilogue, s, 2);
+    MOK_TRY(invert_rows(schedule_peer_rank, schedule_peer_token_idx, num_tokens, route_row, num_local_tokens * topk, row_limit, s));
+    mok::epilogue_rows_kernel<true><<<epilogue_grid(static_cast<int64_t>(num_local_tokens) * vpr), 256, 0, s>>>(
+        static_cast<const uint4*>(y_shared), static_cast<const uint4*>(y_routed), route_row, topk_weights, nullptr, 0, nullptr,
+        static_cast<uint4*>(output), num_local_tokens, vpr, topk);
+    MOK_CUDA_CHECK(cudaGetLastError());
+    return MOK_OK;
+}
+
+extern "C" int mok_bwd_epilogue_rows(const void* d_x_shared, const void* d_x_routed, const float* partials, int partial_cols,
+                                     const int32_t* schedule_peer_rank, const int32_t* schedule_peer_token_idx,
+                                     const int32_t* num_tokens, int32_t* route_row, void* d_x, float* d_router_weights,
+                                     int num_local_tokens, int hidden, int topk, int row_limit, void* stream) {
+    if (!d_x_shared || !d_x_routed || !partials || !schedule_peer_rank || !schedule_peer_token_idx || !num_tokens ||
+        !route_row || !d_x || !d_router_weights)
+        return MOK_ERR_INVALID;
+    if (num_local_tokens <= 0 || hidden <= 0 || hidden % 8 || topk <= 0 || row_limit <= 0 || partial_cols <= 0)
+        return MOK_ERR_INVALID;
+    if (static_cast<int64_t>(num_local_tokens) * topk > INT32_MAX) return MOK_ERR_TOO_LARGE;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int vpr = hidden / 8;
+    ProfScope prof(kSlotEpilogue, s, 2);
+    MOK_TRY(invert_rows(schedule_peer_rank, schedule_peer_token_idx, num_tokens, route_row, num_local_tokens * topk, row_limit, s));
+    mok::epilogue_rows_kernel<false><<<epilogue_grid(static_cast<int64_t>(num_local_tokens) * vpr), 256, 0, s>>>(
+        static_cast<const uint4*>(d_x_shared), static_cast<const uint4*>(d_x_routed), route_row, nullptr, partials, partial_cols,
+        d_router_weights, static_cast<uint4*>(d_x), num_local_tokens, vpr, topk);
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
 }

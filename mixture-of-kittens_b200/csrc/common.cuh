@@ -275,6 +275,7 @@ __device__ __forceinline__ void chunk_range(int win_rows, const ChunkSpec& c, in
     hi = (c.index == c.num_chunks - 1) ? win_rows : min(win_rows, lo + per);
 }
 
+#define MOK_TRY(expr) do { int rc__ = (expr); if (rc__ != MOK_OK) return rc__; } while (0)
 #define MOK_CUDA_CHECK(expr)                                       \
     do {                                                           \
         cudaError_t err__ = (expr);                                \

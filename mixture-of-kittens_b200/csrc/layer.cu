@@ -33,6 +33,8 @@ int check_common(const mok_layer_common& c, Dims& d) {
     if (d.cap <= 0 || d.cap % 256 || d.MB <= 0 || d.MB % 256) return MOK_ERR_INVALID;
     if (c.minibatch_size <= 0 || c.minibatch_size % 256 || d.MB % c.minibatch_size) return MOK_ERR_INVALID;
     if (!c.schedule_peer_rank || !c.schedule_peer_token_idx || !c.num_tokens || !c.tokens_per_expert) return MOK_ERR_INVALID;
+    // results may stay in their rows only when every row is local and one window holds the whole schedule
+    if (c.defer_combine && (d.W != 1 || d.cap > d.MB)) return MOK_ERR_INVALID;
     return MOK_OK;
 }
 
@@ -72,7 +74,6 @@ GemmParams base_params(const mok_layer_common& c, bool routed, int off, int limi
     return p;
 }
 
-#define MOK_TRY(expr) do { int rc__ = (expr); if (rc__ != MOK_OK) return rc__; } while (0)
 
 // gate|up GEMM with fused SwiGLU: A [rows, H] K-major, B = (Wg, Wu) [E*I, H] K-major
 int run_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int off, int limit, const void* a, int a_rows,
@@ -372,6 +373,7 @@ extern "C" int mok_fwd_bf16(const mok_fwd_bf16_args* a, void* stream) {
                 return run_down(c, d, true, off, limit, a->hidden_routed, d.MB, a->w_routed_down, a->y_routed, st);
             },
             [&](cudaStream_t st) {
+                if (c.defer_combine) return static_cast<int>(MOK_OK);   // mok_fwd_epilogue_rows reads y_routed in place
                 RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
                 comb.peers = combine_peers;
                 return launch_combine_rows(comb, move_grid(), st);
@@ -442,6 +444,7 @@ extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
             },
             [&](cudaStream_t st) {
                 RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
+                if (c.defer_combine) return static_cast<int>(MOK_OK);   // mok_bwd_epilogue_rows reads the rows in place
                 rd.peers = dxr_peers;
                 rd.scale_peers = drw_peers;
                 rd.partials = a->d_router_weight_partials;
@@ -600,6 +603,7 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
                                a->w_routed_down_sc, a->y_routed, st);
             },
             [&](cudaStream_t st) {
+                if (c.defer_combine) return static_cast<int>(MOK_OK);   // mok_fwd_epilogue_rows reads y_routed in place
                 RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
                 comb.peers = combine_peers;
                 return launch_combine_rows(comb, move_grid(), st);
@@ -707,6 +711,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
             },
             [&](cudaStream_t st) {
                 RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
+                if (c.defer_combine) return static_cast<int>(MOK_OK);   // mok_bwd_epilogue_rows reads the rows in place
                 rd.peers = dxr_peers;
                 rd.scale_peers = drw_peers;
                 rd.partials = a->d_router_weight_partials;

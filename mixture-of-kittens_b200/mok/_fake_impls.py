@@ -52,7 +52,7 @@ def _(x_bf16, return_normal, return_transposed):
 @_fake("mok::dispatch_mlp_swiglu_combine_fwd_bf16")
 def _(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_routed_gate, w_shared_up, w_routed_up,
       w_shared_down, w_routed_down, schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert,
-      topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+      topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size, defer_combine=False):
     T, H = x.shape
     I, MB = w_shared_gate.shape[0], macrobatch_size
     shapes = ((MB, H), (T, I), (MB, I), (T, I), (MB, I), (T, I), (MB, I), (T, H), (MB, H))
@@ -64,7 +64,7 @@ def _(d_y_buffer, d_y_buffer_ptrs, d_x_routed_buffer, d_x_routed_buffer_ptrs, ro
       router_weight_buffer_ptrs, d_router_weight_buffer, d_router_weight_buffer_ptrs, w_shared_gate, w_routed_gate,
       w_shared_up, w_routed_up, w_shared_down, w_routed_down, x_routed, gate_shared, gate_routed, up_shared, up_routed,
       hidden_shared, hidden_routed, x, x_ptrs, schedule_peer_rank, schedule_peer_token_idx, num_tokens,
-      tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+      tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size, defer_combine=False):
     T, H = x.shape
     I, El, MB = w_shared_gate.shape[0], w_routed_gate.shape[0], macrobatch_size
     shapes = ((T, H), (MB, H), (T, I), (MB, I), (T, I), (MB, I), (T, I), (MB, I), (MB, H),
@@ -77,6 +77,11 @@ def _(y_shared, combine_buffer, topk_weights):
     return torch.empty_like(y_shared)
 
 
+@_fake("mok::fwd_epilogue_rows")
+def _(y_shared, y_routed, schedule_peer_rank, schedule_peer_token_idx, num_tokens, topk_weights):
+    return torch.empty_like(y_shared)
+
+
 @_fake("mok::bwd_epilogue")
 def _(d_x_shared, d_x_routed_buffer):
     return torch.empty_like(d_x_shared)
@@ -86,7 +91,7 @@ def _(d_x_shared, d_x_routed_buffer):
 def _(x, x_ptrs, combine_buffer, combine_buffer_ptrs, w_shared_gate, w_routed_gate, w_routed_gate_sc, w_shared_up,
       w_routed_up, w_routed_up_sc, w_shared_down, w_routed_down, w_routed_down_sc, schedule_peer_rank,
       schedule_peer_token_idx, num_tokens, tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size,
-      minibatch_size):
+      minibatch_size, defer_combine=False):
     T, H = x.shape
     I, MB = w_shared_gate.shape[0], macrobatch_size
     spec = (((H, MB), _FP8), (_sc(H, MB), _U8), ((T, I), _BF16), ((MB, I), _FP8), (_sc(MB, I), _U8), ((T, I), _BF16),
@@ -102,7 +107,7 @@ def _(d_y_buffer, d_y_buffer_ptrs, d_x_routed_buffer, d_x_routed_buffer_ptrs, ro
       w_routed_down_T_sc, x_fp8_t_routed, x_sc_t_routed, gate_shared, gate_fp8_routed, gate_sc_routed, up_shared,
       up_fp8_routed, up_sc_routed, hidden_shared, hidden_fp8_t_routed, hidden_sc_t_routed, x, x_ptrs, w_routed_gate,
       w_routed_gate_sc, w_routed_up, w_routed_up_sc, schedule_peer_rank, schedule_peer_token_idx, num_tokens,
-      tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size):
+      tokens_per_expert, topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size, defer_combine=False):
     T, H = x.shape
     I, El, MB = w_shared_gate.shape[0], w_routed_gate.shape[0], macrobatch_size
     spec = (((T, H), _BF16), ((MB, H), _BF16), ((T, I), _BF16), ((MB, I), _FP8), (_sc(MB, I), _U8), ((T, I), _BF16),

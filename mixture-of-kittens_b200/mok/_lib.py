@@ -47,7 +47,7 @@ class LayerCommon(C.Structure):
         ("num_local_experts", C.c_int), ("topk", C.c_int),
         ("schedule_capacity", C.c_int), ("macrobatch_size", C.c_int), ("minibatch_size", C.c_int),
         ("num_comm_sms", C.c_int),
-        ("has_swiglu_limit", C.c_int), ("swiglu_limit", C.c_float),
+        ("has_swiglu_limit", C.c_int), ("swiglu_limit", C.c_float), ("defer_combine", C.c_int),
         ("schedule_peer_rank", vp), ("schedule_peer_token_idx", vp),
         ("num_tokens", vp), ("tokens_per_expert", vp), ("status", vp),
     ]
@@ -130,6 +130,10 @@ mok_schedule_static = _sig("mok_schedule_static", C.c_int, [vp, C.c_int, C.c_int
 mok_mxfp8_quantize = _sig("mok_mxfp8_quantize", C.c_int, [vp, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp, vp])
 mok_fwd_epilogue = _sig("mok_fwd_epilogue", C.c_int, [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp])
 mok_bwd_epilogue = _sig("mok_bwd_epilogue", C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp])
+mok_fwd_epilogue_rows = _sig("mok_fwd_epilogue_rows", C.c_int,
+                             [vp, vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp])
+mok_bwd_epilogue_rows = _sig("mok_bwd_epilogue_rows", C.c_int,
+                             [vp, vp, vp, C.c_int, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp])
 mok_fwd_bf16 = _sig("mok_fwd_bf16", C.c_int, [C.POINTER(FwdBf16Args), vp])
 mok_bwd_bf16 = _sig("mok_bwd_bf16", C.c_int, [C.POINTER(BwdBf16Args), vp])
 mok_fwd_mxfp8 = _sig("mok_fwd_mxfp8", C.c_int, [C.POINTER(FwdMxfp8Args), vp])

@@ -15,6 +15,7 @@ Differences a caller can observe:
 """
 from __future__ import annotations
 
+import os
 import math
 from dataclasses import dataclass
 from typing import Any
@@ -26,6 +27,11 @@ from . import _lib
 from . import ops
 
 _SUPPORTED_EP_SIZES = (1, 2, 4, 8)
+
+# With one rank no peer reads this rank's buffers: skip the staging copies, the barriers and, when one macrobatch
+# holds the whole schedule, the combine pass.  MOK_B200_LOCAL_FAST_PATH=0 keeps the multi-rank sequence (tests
+# compare the two bit for bit).
+SINGLE_RANK_FAST_PATH = os.environ.get("MOK_B200_LOCAL_FAST_PATH", "1") != "0"
 
 
 @dataclass(frozen=True, slots=True)
@@ -289,12 +295,16 @@ def build_schedule(workspace: MoKWorkspace, config: MoKConfig, top_experts: torc
     if type(num_local_experts) is not int or num_local_experts <= 0:
         raise ValueError("num_local_experts must be a positive integer")
 
-    ops.all_gather_top_experts(top_experts.to(torch.int32), workspace.all_gather_top_experts_buffer,
-                               workspace.all_gather_top_experts_buffer_multicast_ptr, workspace.ep_rank,
-                               config.all_gather_top_experts_chunk_bytes)
-    _barrier(workspace)
+    if workspace.ep_size == 1 and SINGLE_RANK_FAST_PATH:           # nothing to gather: the scheduler reads the routes where the cast put them
+        topk_all = top_experts.to(torch.int32).unsqueeze(0)
+    else:
+        ops.all_gather_top_experts(top_experts.to(torch.int32), workspace.all_gather_top_experts_buffer,
+                                   workspace.all_gather_top_experts_buffer_multicast_ptr, workspace.ep_rank,
+                                   config.all_gather_top_experts_chunk_bytes)
+        _barrier(workspace)
+        topk_all = workspace.all_gather_top_experts_buffer
     peer_rank, peer_token_idx, num_tokens, tokens_per_expert = ops.schedule(
-        workspace.all_gather_top_experts_buffer, num_local_experts, workspace.schedule_capacity, workspace.ep_rank)
+        topk_all, num_local_experts, workspace.schedule_capacity, workspace.ep_rank)
     return MoKSchedule(peer_rank=peer_rank, peer_token_idx=peer_token_idx, num_tokens=num_tokens,
                        tokens_per_expert=tokens_per_expert)
 
@@ -337,17 +347,26 @@ def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x
     """
     validate_inputs(config, workspace, schedule, x, router_weights)
     ws = workspace
-    ws.x_buffer.copy_(x)
-    ws.router_weight_buffer.copy_(router_weights)
-    _barrier(ws)
+    # Single rank: no peer reads this rank's buffers, so the kernels work on the caller's tensors (no staging
+    # copies, no barriers), and when one macrobatch holds the whole schedule the routed rows are summed straight
+    # from the down-GEMM output instead of going through the combine buffer.
+    local = ws.ep_size == 1 and SINGLE_RANK_FAST_PATH
+    defer = local and ws.schedule_capacity <= config.macrobatch_size
+    if local:
+        x_buf, x_ptrs, rw_buf = x, ops.SELF_PTRS, router_weights
+    else:
+        ws.x_buffer.copy_(x)
+        ws.router_weight_buffer.copy_(router_weights)
+        _barrier(ws)
+        x_buf, x_ptrs, rw_buf = ws.x_buffer, ws.x_buffer_ptrs, ws.router_weight_buffer
     sched = (schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens, schedule.tokens_per_expert)
-    knobs = (ws.topk, swiglu_limit, config.fwd_num_comm_sms, config.macrobatch_size, config.minibatch_size)
+    knobs = (ws.topk, swiglu_limit, config.fwd_num_comm_sms, config.macrobatch_size, config.minibatch_size, defer)
 
     if isinstance(routed_gate_weights, tuple):
         (g_q, g_s), (u_q, u_s), (d_q, d_s) = routed_gate_weights, routed_up_weights, routed_down_weights
         (x_t_q, x_t_s, gate_sh, gate_q, gate_s, up_sh, up_q, up_s, hid_sh, hid_t_q, hid_t_s,
-         y_shared, _y_routed) = ops.dispatch_mlp_swiglu_combine_fwd_mxfp8(
-            ws.x_buffer, ws.x_buffer_ptrs, ws.combine_buffer, ws.combine_buffer_ptrs,
+         y_shared, y_routed) = ops.dispatch_mlp_swiglu_combine_fwd_mxfp8(
+            x_buf, x_ptrs, ws.combine_buffer, ws.combine_buffer_ptrs,
             shared_gate_weights, g_q, g_s, shared_up_weights, u_q, u_s, shared_down_weights, d_q, d_s,
             *sched, *knobs)
         ctx = MoKForwardContext(x_routed=(x_t_q, x_t_s), gate_shared=gate_sh, gate_routed=(gate_q, gate_s),
@@ -355,15 +374,20 @@ def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x
                                 hidden_routed=(hid_t_q, hid_t_s))
     else:
         (x_routed, gate_sh, gate_r, up_sh, up_r, hid_sh, hid_r,
-         y_shared, _y_routed) = ops.dispatch_mlp_swiglu_combine_fwd_bf16(
-            ws.x_buffer, ws.x_buffer_ptrs, ws.combine_buffer, ws.combine_buffer_ptrs,
+         y_shared, y_routed) = ops.dispatch_mlp_swiglu_combine_fwd_bf16(
+            x_buf, x_ptrs, ws.combine_buffer, ws.combine_buffer_ptrs,
             shared_gate_weights, routed_gate_weights, shared_up_weights, routed_up_weights,
             shared_down_weights, routed_down_weights, *sched, *knobs)
         ctx = MoKForwardContext(x_routed=x_routed, gate_shared=gate_sh, gate_routed=gate_r, up_shared=up_sh,
                                 up_routed=up_r, hidden_shared=hid_sh, hidden_routed=hid_r)
 
-    _barrier(ws)
-    output = ops.fwd_epilogue(y_shared, ws.combine_buffer, ws.router_weight_buffer)
+    if defer:
+        output = ops.fwd_epilogue_rows(y_shared, y_routed, schedule.peer_rank, schedule.peer_token_idx,
+                                       schedule.num_tokens, rw_buf)
+    else:
+        if not local:
+            _barrier(ws)
+        output = ops.fwd_epilogue(y_shared, ws.combine_buffer, rw_buf)
     return output, ctx
 
 
@@ -381,14 +405,21 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
     if not isinstance(forward_context, MoKForwardContext):
         raise TypeError("forward_context must be a MoKForwardContext")
     ws, ctx = workspace, forward_context
-    ws.d_y_buffer.copy_(grad_output)
-    ws.x_buffer.copy_(x)
-    ws.router_weight_buffer.copy_(router_weights)
-    _barrier(ws)
+    local = ws.ep_size == 1 and SINGLE_RANK_FAST_PATH              # see forward
+    defer = local and ws.schedule_capacity <= config.macrobatch_size
+    if local:
+        d_y_buf, d_y_ptrs, x_buf, x_ptrs = grad_output, ops.SELF_PTRS, x, ops.SELF_PTRS
+        rw_buf, rw_ptrs = router_weights, ops.SELF_PTRS
+    else:
+        ws.d_y_buffer.copy_(grad_output)
+        ws.x_buffer.copy_(x)
+        ws.router_weight_buffer.copy_(router_weights)
+        _barrier(ws)
+        d_y_buf, d_y_ptrs, x_buf, x_ptrs = ws.d_y_buffer, ws.d_y_buffer_ptrs, ws.x_buffer, ws.x_buffer_ptrs
+        rw_buf, rw_ptrs = ws.router_weight_buffer, ws.router_weight_buffer_ptrs
     sched = (schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens, schedule.tokens_per_expert)
-    knobs = (ws.topk, swiglu_limit, config.bwd_num_comm_sms, config.macrobatch_size, config.minibatch_size)
-    buffers = (ws.d_y_buffer, ws.d_y_buffer_ptrs, ws.d_x_routed_buffer, ws.d_x_routed_buffer_ptrs,
-               ws.router_weight_buffer, ws.router_weight_buffer_ptrs,
+    knobs = (ws.topk, swiglu_limit, config.bwd_num_comm_sms, config.macrobatch_size, config.minibatch_size, defer)
+    buffers = (d_y_buf, d_y_ptrs, ws.d_x_routed_buffer, ws.d_x_routed_buffer_ptrs, rw_buf, rw_ptrs,
                ws.d_router_weight_buffer, ws.d_router_weight_buffer_ptrs)
 
     if isinstance(routed_gate_weights, tuple):
@@ -400,7 +431,7 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
             shared_gate_weights, g_t_q, g_t_s, shared_up_weights, u_t_q, u_t_s, shared_down_weights, d_t_q, d_t_s,
             *ctx.x_routed, ctx.gate_shared, *ctx.gate_routed, ctx.up_shared, *ctx.up_routed,
             ctx.hidden_shared, *ctx.hidden_routed,
-            ws.x_buffer, ws.x_buffer_ptrs, g_q, g_s, u_q, u_s, *sched, *knobs)
+            x_buf, x_ptrs, g_q, g_s, u_q, u_s, *sched, *knobs)
         d_x_shared = res[0]
         d_w_sh_gate, d_w_r_gate, d_w_sh_up, d_w_r_up, d_w_sh_down, d_w_r_down = res[12:18]
     else:
@@ -409,11 +440,15 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
             shared_gate_weights, routed_gate_weights, shared_up_weights, routed_up_weights,
             shared_down_weights, routed_down_weights,
             ctx.x_routed, ctx.gate_shared, ctx.gate_routed, ctx.up_shared, ctx.up_routed,
-            ctx.hidden_shared, ctx.hidden_routed, ws.x_buffer, ws.x_buffer_ptrs, *sched, *knobs)
+            ctx.hidden_shared, ctx.hidden_routed, x_buf, x_ptrs, *sched, *knobs)
         d_x_shared = res[0]
         d_w_sh_gate, d_w_r_gate, d_w_sh_up, d_w_r_up, d_w_sh_down, d_w_r_down = res[9:15]
 
-    _barrier(ws)
-    d_x = ops.bwd_epilogue(d_x_shared, ws.d_x_routed_buffer)
+    if defer:                            # the op summed the routed rows in place: its first output is d_x already
+        d_x = d_x_shared
+    else:
+        if not local:
+            _barrier(ws)
+        d_x = ops.bwd_epilogue(d_x_shared, ws.d_x_routed_buffer)
     d_router_weights = ws.d_router_weight_buffer.clone()
     return (d_x, d_router_weights, d_w_r_gate, d_w_r_up, d_w_r_down, d_w_sh_gate, d_w_sh_up, d_w_sh_down)

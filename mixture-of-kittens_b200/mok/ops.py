@@ -48,6 +48,15 @@ def _layer_scalars(topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_
           "macrobatch_size must be a positive multiple of minibatch_size")
 
 
+# A pointer list equal to SELF_PTRS stands for "one rank: the address of the tensor passed beside it".  It keeps
+# data_ptr() calls out of the caller, so the single-rank path stays traceable by torch.compile.
+SELF_PTRS = [-1]
+
+
+def _self_ptrs(local: Tensor, ptrs: list[int]) -> list[int]:
+    return [local.data_ptr()] if list(ptrs) == SELF_PTRS else ptrs
+
+
 def _pointer_lists(named: dict[str, list[int]], lead: str) -> int:
     for name, ptrs in named.items():
         ok = isinstance(ptrs, list) and all(type(p) is int and p > 0 for p in ptrs)
@@ -95,7 +104,7 @@ def _vp(t: Tensor | None) -> int | None:
 
 
 def _common(x: Tensor, ep_size: int, inter: int, n_experts: int, topk: int, cap: int, macro: int, mini: int,
-            comm_sms: int, limit, sched) -> _lib.LayerCommon:
+            comm_sms: int, limit, sched, defer_combine: bool = False) -> _lib.LayerCommon:
     peer_rank, peer_tok, num_tokens, tokens_per_expert = sched
     for name, t in (("schedule_peer_rank", peer_rank), ("schedule_peer_token_idx", peer_tok),
                     ("num_tokens", num_tokens), ("tokens_per_expert", tokens_per_expert)):
@@ -108,6 +117,10 @@ def _common(x: Tensor, ep_size: int, inter: int, n_experts: int, topk: int, cap:
     c.schedule_capacity, c.macrobatch_size, c.minibatch_size, c.num_comm_sms = cap, macro, mini, comm_sms
     c.has_swiglu_limit = 0 if limit is None else 1
     c.swiglu_limit = 0.0 if limit is None else float(limit)
+    if defer_combine:
+        _need(ep_size == 1 and cap <= macro,
+              "defer_combine needs a single rank and a schedule capacity within one macrobatch")
+    c.defer_combine = 1 if defer_combine else 0
     c.schedule_peer_rank, c.schedule_peer_token_idx = peer_rank.data_ptr(), peer_tok.data_ptr()
     c.num_tokens, c.tokens_per_expert = num_tokens.data_ptr(), tokens_per_expert.data_ptr()
     c.status = _lib.status_tensor(x.device).data_ptr()
@@ -267,7 +280,9 @@ def dispatch_mlp_swiglu_combine_fwd_bf16(
     w_shared_down: Tensor, w_routed_down: Tensor,
     schedule_peer_rank: Tensor, schedule_peer_token_idx: Tensor, num_tokens: Tensor, tokens_per_expert: Tensor,
     topk: int, swiglu_limit: float | None, num_comm_sms: int, macrobatch_size: int, minibatch_size: int,
+    defer_combine: bool = False,
 ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    x_ptrs = _self_ptrs(x, x_ptrs)
     T, H = _token_hidden(x, "x")
     I = _intermediate(w_shared_gate, H, strict_cols=True)
     El = _local_experts(w_routed_gate)
@@ -296,7 +311,7 @@ def dispatch_mlp_swiglu_combine_fwd_bf16(
 
     a = _lib.FwdBf16Args()
     a.c = _common(x, ep_size, I, El, topk, cap, MB, minibatch_size, num_comm_sms, swiglu_limit,
-                  (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert))
+                  (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert), defer_combine)
     a.c.ep_rank = _own_rank(x, x_ptrs, "x_ptrs")
     xp, cp = _lib.ptr_array(x_ptrs), _lib.ptr_array(combine_buffer_ptrs)
     a.x_ptrs, a.combine_buffer_ptrs = xp, cp
@@ -326,8 +341,11 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(
     hidden_shared: Tensor, hidden_routed: Tensor, x: Tensor, x_ptrs: list[int],
     schedule_peer_rank: Tensor, schedule_peer_token_idx: Tensor, num_tokens: Tensor, tokens_per_expert: Tensor,
     topk: int, swiglu_limit: float | None, num_comm_sms: int, macrobatch_size: int, minibatch_size: int,
+    defer_combine: bool = False,
 ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor,
            Tensor, Tensor]:
+    x_ptrs, d_y_buffer_ptrs = _self_ptrs(x, x_ptrs), _self_ptrs(d_y_buffer, d_y_buffer_ptrs)
+    router_weight_buffer_ptrs = _self_ptrs(router_weight_buffer, router_weight_buffer_ptrs)
     T, H = _token_hidden(x, "x")
     I = _intermediate(w_shared_gate, H, strict_cols=True)
     El = _local_experts(w_routed_gate)
@@ -376,7 +394,7 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(
 
     a = _lib.BwdBf16Args()
     a.c = _common(x, ep_size, I, El, topk, cap, MB, minibatch_size, num_comm_sms, swiglu_limit,
-                  (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert))
+                  (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert), defer_combine)
     a.c.ep_rank = _own_rank(x, x_ptrs, "x_ptrs")
     keep = [_lib.ptr_array(p) for p in (d_y_buffer_ptrs, d_x_routed_buffer_ptrs, router_weight_buffer_ptrs,
                                         d_router_weight_buffer_ptrs, x_ptrs)]
@@ -393,6 +411,12 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(
     a.d_w_routed_gate, a.d_w_routed_up, a.d_w_routed_down = (t.data_ptr() for t in (d_w_routed_gate, d_w_routed_up, d_w_routed_down))
     a.router_weights_routed, a.d_router_weight_partials = row_weights.data_ptr(), partials.data_ptr()
     _lib.check(_lib.mok_bwd_bf16(a, _lib.stream_ptr(dev)), "dispatch_mlp_swiglu_combine_bwd_bf16")
+    if defer_combine:      # no combine ran: gather the rows here; d_x_shared becomes d_x, the router gradients land in the buffer
+        route_row = torch.empty(T * topk, dtype=torch.int32, device=dev)
+        _lib.check(_lib.mok_bwd_epilogue_rows(
+            d_x_shared.data_ptr(), d_x_routed.data_ptr(), partials.data_ptr(), partials.shape[1], schedule_peer_rank.data_ptr(),
+            schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(), route_row.data_ptr(), d_x_shared.data_ptr(),
+            d_router_weight_buffer.data_ptr(), T, H, topk, MB, _lib.stream_ptr(dev)), "bwd_epilogue_rows")
     return (d_x_shared, d_x_routed, d_gate_shared, d_gate_routed, d_up_shared, d_up_routed, d_hidden_shared,
             d_hidden_routed, d_y_routed, d_w_shared_gate, d_w_routed_gate, d_w_shared_up, d_w_routed_up,
             d_w_shared_down, d_w_routed_down)
@@ -416,6 +440,41 @@ def fwd_epilogue(y_shared: Tensor, combine_buffer: Tensor, topk_weights: Tensor)
     out = torch.empty_like(y_shared)
     _lib.check(_lib.mok_fwd_epilogue(y_shared.data_ptr(), combine_buffer.data_ptr(), topk_weights.data_ptr(),
                                      out.data_ptr(), T, H, topk, _lib.stream_ptr(y_shared.device)), "fwd_epilogue")
+    return out
+
+
+@torch.library.custom_op("mok::fwd_epilogue_rows", mutates_args=())
+def fwd_epilogue_rows(y_shared: Tensor, y_routed: Tensor, schedule_peer_rank: Tensor, schedule_peer_token_idx: Tensor,
+                      num_tokens: Tensor, topk_weights: Tensor) -> Tensor:
+    """Single-rank forward epilogue that reads the routed rows where the down GEMM left them.
+
+    Follows a forward op called with ``defer_combine=True``; gives the bytes ``fwd_epilogue`` gives after a
+    combine.  No reference counterpart (the reference always goes through the combine buffer,
+    mok/functional.py:569-571)."""
+    T, H = _token_hidden(y_shared, "y_shared")
+    _need(topk_weights.ndim == 2 and topk_weights.shape[0] == T, "topk_weights must have shape (num_local_tokens, topk)")
+    topk = topk_weights.shape[1]
+    _need(0 < topk <= 255, "topk must be in [1, 255]")
+    _need(y_routed.ndim == 2 and y_routed.shape[1] == H and y_routed.shape[0] > 0,
+          "y_routed must have shape (macrobatch_size, hidden_size)")
+    for name, t in (("y_routed", y_routed), ("schedule_peer_rank", schedule_peer_rank),
+                    ("schedule_peer_token_idx", schedule_peer_token_idx), ("num_tokens", num_tokens),
+                    ("topk_weights", topk_weights)):
+        _need(t.device == y_shared.device, f"{name} must be on the same CUDA device as y_shared")
+    _bf16({"y_shared": y_shared, "y_routed": y_routed})
+    _need(topk_weights.dtype == torch.float32 and topk_weights.is_contiguous(),
+          "topk_weights must be contiguous float32", TypeError)
+    for name, t in (("schedule_peer_rank", schedule_peer_rank), ("schedule_peer_token_idx", schedule_peer_token_idx),
+                    ("num_tokens", num_tokens)):
+        _need(t.dtype == torch.int32 and t.is_contiguous(), f"{name} must be contiguous int32", TypeError)
+    _need(schedule_peer_rank.numel() == schedule_peer_token_idx.numel() and schedule_peer_rank.numel() <= y_routed.shape[0],
+          "the schedule must fit in y_routed")
+    out = torch.empty_like(y_shared)
+    route_row = torch.empty(T * topk, dtype=torch.int32, device=y_shared.device)
+    _lib.check(_lib.mok_fwd_epilogue_rows(
+        y_shared.data_ptr(), y_routed.data_ptr(), schedule_peer_rank.data_ptr(), schedule_peer_token_idx.data_ptr(),
+        num_tokens.data_ptr(), topk_weights.data_ptr(), route_row.data_ptr(), out.data_ptr(), T, H, topk,
+        schedule_peer_rank.numel(), _lib.stream_ptr(y_shared.device)), "fwd_epilogue_rows")
     return out
 
 
@@ -455,7 +514,9 @@ def dispatch_mlp_swiglu_combine_fwd_mxfp8(
     w_shared_down: Tensor, w_routed_down: Tensor, w_routed_down_sc: Tensor,
     schedule_peer_rank: Tensor, schedule_peer_token_idx: Tensor, num_tokens: Tensor, tokens_per_expert: Tensor,
     topk: int, swiglu_limit: float | None, num_comm_sms: int, macrobatch_size: int, minibatch_size: int,
+    defer_combine: bool = False,
 ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor]:
+    x_ptrs = _self_ptrs(x, x_ptrs)
     T, H = _token_hidden(x, "x")
     _layer_scalars(topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size)
     ep_size = _pointer_lists({"x_ptrs": x_ptrs, "combine_buffer_ptrs": combine_buffer_ptrs}, "x_ptrs")
@@ -498,7 +559,7 @@ def dispatch_mlp_swiglu_combine_fwd_mxfp8(
 
     a = _lib.FwdMxfp8Args()
     a.c = _common(x, ep_size, I, El, topk, cap, MB, minibatch_size, num_comm_sms, swiglu_limit,
-                  (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert))
+                  (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert), defer_combine)
     a.c.ep_rank = _own_rank(x, x_ptrs, "x_ptrs")
     keep = (_lib.ptr_array(x_ptrs), _lib.ptr_array(combine_buffer_ptrs))
     a.x_ptrs, a.combine_buffer_ptrs = keep
@@ -537,8 +598,11 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
     w_routed_gate: Tensor, w_routed_gate_sc: Tensor, w_routed_up: Tensor, w_routed_up_sc: Tensor,
     schedule_peer_rank: Tensor, schedule_peer_token_idx: Tensor, num_tokens: Tensor, tokens_per_expert: Tensor,
     topk: int, swiglu_limit: float | None, num_comm_sms: int, macrobatch_size: int, minibatch_size: int,
+    defer_combine: bool = False,
 ) -> tuple[Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor, Tensor,
            Tensor, Tensor, Tensor, Tensor, Tensor]:
+    x_ptrs, d_y_buffer_ptrs = _self_ptrs(x, x_ptrs), _self_ptrs(d_y_buffer, d_y_buffer_ptrs)
+    router_weight_buffer_ptrs = _self_ptrs(router_weight_buffer, router_weight_buffer_ptrs)
     T, H = _token_hidden(x, "x")
     _layer_scalars(topk, swiglu_limit, num_comm_sms, macrobatch_size, minibatch_size)
     ep_size = _pointer_lists({"x_ptrs": x_ptrs, "d_y_buffer_ptrs": d_y_buffer_ptrs,
@@ -612,7 +676,7 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
 
     a = _lib.BwdMxfp8Args()
     a.c = _common(x, ep_size, I, El, topk, cap, MB, minibatch_size, num_comm_sms, swiglu_limit,
-                  (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert))
+                  (schedule_peer_rank, schedule_peer_token_idx, num_tokens, tokens_per_expert), defer_combine)
     a.c.ep_rank = _own_rank(x, x_ptrs, "x_ptrs")
     keep = [_lib.ptr_array(p) for p in (d_y_buffer_ptrs, d_x_routed_buffer_ptrs, router_weight_buffer_ptrs,
                                         d_router_weight_buffer_ptrs, x_ptrs)]
@@ -635,6 +699,12 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
     for k, t in fields.items():
         setattr(a, k, t.data_ptr())
     _lib.check(_lib.mok_bwd_mxfp8(a, _lib.stream_ptr(dev)), "dispatch_mlp_swiglu_combine_bwd_mxfp8")
+    if defer_combine:      # no combine ran: gather the rows here; d_x_shared becomes d_x, the router gradients land in the buffer
+        route_row = torch.empty(T * topk, dtype=torch.int32, device=dev)
+        _lib.check(_lib.mok_bwd_epilogue_rows(
+            d_x_shared.data_ptr(), d_x_routed.data_ptr(), work["d_router_weight_partials"].data_ptr(), work["d_router_weight_partials"].shape[1], schedule_peer_rank.data_ptr(),
+            schedule_peer_token_idx.data_ptr(), num_tokens.data_ptr(), route_row.data_ptr(), d_x_shared.data_ptr(),
+            d_router_weight_buffer.data_ptr(), T, H, topk, MB, _lib.stream_ptr(dev)), "bwd_epilogue_rows")
     return (d_x_shared, d_x_routed, d_gate_shared, d_gate_q, d_gate_sc, d_up_shared, d_up_q, d_up_sc,
             d_hidden_shared, d_hidden_routed, d_y_q, d_y_sc, d_w_shared_gate, d_w_routed_gate, d_w_shared_up,
             d_w_routed_up, d_w_shared_down, d_w_routed_down)

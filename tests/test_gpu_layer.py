@@ -89,6 +89,21 @@ def test_multiple_macrobatches_replay(cuda_device, single_rank_group):
         assert rel_l2(ref[name].float(), many[name].float()) < BF16_REL_L2, name
 
 
+@pytest.mark.parametrize("mxfp8", [False, True])
+def test_single_rank_fast_path_is_bit_identical(cuda_device, single_rank_group, monkeypatch, mxfp8):
+    """Gathering the routed rows in the epilogue (no staging copies, barriers or combine pass) gives the bytes
+    of the multi-rank sequence run on one rank."""
+    import mok
+    cfg = dict(T=1024, H=512, I=512, E=8, W=1, K=4)
+    inp = O.make_rank_inputs(0, seed=17, **cfg)
+    fast = run_layer(cuda_device, single_rank_group, inp, mxfp8=mxfp8, limit=7.0)
+    monkeypatch.setattr(mok.functional, "SINGLE_RANK_FAST_PATH", False)
+    slow = run_layer(cuda_device, single_rank_group, inp, mxfp8=mxfp8, limit=7.0)
+    assert torch.equal(fast["output"], slow["output"])
+    for name in GRAD_NAMES:
+        assert torch.equal(fast[name], slow[name]), name
+
+
 def test_two_runs_are_bit_identical(cuda_device, single_rank_group):
     cfg = dict(T=1024, H=512, I=512, E=8, W=1, K=4)
     inp = O.make_rank_inputs(0, seed=13, **cfg)
