@@ -99,6 +99,22 @@ int mok_fwd_epilogue(const void* y_shared, const void* combine_buffer, const flo
 int mok_bwd_epilogue(const void* d_x_shared, const void* d_x_routed_buffer, void* d_x,
                      int num_local_tokens, int hidden, int topk, void* stream);
 
+/* Router in front of the path: for every token the K largest logits (descending, lower expert index first among
+ * equal values) and the softmax over those K values = softmax over all experts, top-K, renormalise.
+ * logits f32 [num_tokens, num_experts] (num_experts <= 1024, topk <= 32).  Outputs, each optional except the
+ * weights: top_experts_i32 [T,K], top_experts_i64 [T,K] (the dtype build_schedule takes), router_weights f32 [T,K];
+ * with all_gather_ptrs (ep_size addresses of the [ep_size, T, K] int32 all-gather buffers) the int32 routes are also
+ * written into slot ep_rank of every rank's buffer, which replaces the cast + mok_all_gather_top_experts of
+ * build_schedule (a barrier must still follow before mok_schedule reads the buffer).
+ * mok_router_topk_bwd: d_logits f32 [T, E] (fully written) from d_router_weights.
+ * No reference counterpart: the reference takes finished routes (mok/functional.py:354-430); its tests build them
+ * with torch.topk + softmax (tests/utils.py:82-84), which is the law implemented here. */
+int mok_router_topk(const float* logits, int num_tokens, int num_experts, int topk, int32_t* top_experts_i32,
+                    int64_t* top_experts_i64, float* router_weights, const uint64_t* all_gather_ptrs, int ep_size,
+                    int ep_rank, void* stream);
+int mok_router_topk_bwd(const int32_t* top_experts_i32, const float* router_weights, const float* d_router_weights,
+                        float* d_logits, int num_tokens, int num_experts, int topk, void* stream);
+
 /* Single-rank epilogues that gather the routed rows through the schedule instead of reading a combine buffer:
  *   out[t] = bf16(y_shared[t] + sum_k w[t,k] * y_routed[row(t,k)])            (forward)
  *   d_x[t] = bf16(d_x_shared[t] + sum_k d_x_routed[row(t,k)]),

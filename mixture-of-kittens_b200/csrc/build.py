@@ -14,7 +14,7 @@ CSRC = os.path.dirname(os.path.abspath(__file__))
 PKG = os.path.dirname(CSRC)
 LIB_DIR = os.path.join(PKG, "lib")
 LIB = os.path.join(LIB_DIR, "libmok_b200.so")
-SOURCES = ["scheduler.cu", "quantize.cu", "comm.cu", "gemm.cu", "mxgemm.cu", "layer.cu", "profile.cu"]
+SOURCES = ["scheduler.cu", "quantize.cu", "comm.cu", "gemm.cu", "mxgemm.cu", "layer.cu", "router.cu", "profile.cu"]
 NVCC = os.environ.get("MOK_NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
          "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr", "-Xptxas", "-v"]

@@ -10,8 +10,9 @@ from . import _lib as _lib
 from . import ops as ops
 from . import _fake_impls as _fake_impls
 from . import functional as functional
+from . import nn as nn
 from ._lib import last_status, raise_for_status
 
 __version__ = "0.1.0"
 
-__all__ = ["__version__", "functional", "ops", "last_status", "raise_for_status"]
+__all__ = ["__version__", "functional", "nn", "ops", "last_status", "raise_for_status"]

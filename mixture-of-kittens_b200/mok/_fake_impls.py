@@ -115,3 +115,20 @@ def _(d_y_buffer, d_y_buffer_ptrs, d_x_routed_buffer, d_x_routed_buffer_ptrs, ro
             ((I, H), _BF16), ((El, I, H), _BF16), ((I, H), _BF16), ((El, I, H), _BF16), ((H, I), _BF16),
             ((El, H, I), _BF16))
     return tuple(_new(x, s, dt) for s, dt in spec)
+
+
+@_fake("mok::router_topk")
+def _(logits, topk):
+    T = logits.shape[0]
+    return _new(logits, (T, topk), torch.int64), _new(logits, (T, topk), torch.float32)
+
+
+@_fake("mok::router_topk_gather")
+def _(logits, topk, all_gather_top_experts_buffer, rank):
+    T = logits.shape[0]
+    return _new(logits, (T, topk), torch.int64), _new(logits, (T, topk), torch.float32)
+
+
+@_fake("mok::router_topk_bwd")
+def _(top_experts, router_weights, d_router_weights, num_experts):
+    return _new(router_weights, (top_experts.shape[0], num_experts), torch.float32)

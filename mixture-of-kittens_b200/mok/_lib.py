@@ -130,6 +130,8 @@ mok_schedule_static = _sig("mok_schedule_static", C.c_int, [vp, C.c_int, C.c_int
 mok_mxfp8_quantize = _sig("mok_mxfp8_quantize", C.c_int, [vp, C.c_int, C.c_int, C.c_int, vp, vp, vp, vp, vp])
 mok_fwd_epilogue = _sig("mok_fwd_epilogue", C.c_int, [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp])
 mok_bwd_epilogue = _sig("mok_bwd_epilogue", C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, vp])
+mok_router_topk = _sig("mok_router_topk", C.c_int, [vp, C.c_int, C.c_int, C.c_int, vp, vp, vp, u64p, C.c_int, C.c_int, vp])
+mok_router_topk_bwd = _sig("mok_router_topk_bwd", C.c_int, [vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, vp])
 mok_fwd_epilogue_rows = _sig("mok_fwd_epilogue_rows", C.c_int,
                              [vp, vp, vp, vp, vp, vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, vp])
 mok_bwd_epilogue_rows = _sig("mok_bwd_epilogue_rows", C.c_int,

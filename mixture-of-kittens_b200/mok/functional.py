@@ -312,6 +312,57 @@ def build_schedule(workspace: MoKWorkspace, config: MoKConfig, top_experts: torc
 schedule = build_schedule
 
 
+def route(logits: torch.Tensor, topk: int) -> tuple[torch.Tensor, torch.Tensor]:
+    """Router in front of the layer: (top_experts int64 [T, K], router_weights f32 [T, K]) from f32 logits
+    [T, num_experts] — the K largest logits per token, descending, and the softmax over them (softmax over all
+    experts, top-K, renormalise).  Differentiable with respect to the logits."""
+    return ops.router_topk(logits, topk)
+
+
+class _RouteGather(torch.autograd.Function):
+    """router_topk_gather on the autograd tape (an operator that writes into a buffer cannot carry a registered
+    gradient formula, so the formula sits here)."""
+
+    @staticmethod
+    def forward(ctx, logits, topk, buffer, rank):
+        experts, weights = ops.router_topk_gather(logits, topk, buffer, rank)
+        ctx.save_for_backward(experts, weights)
+        ctx.num_experts = logits.shape[1]
+        ctx.mark_non_differentiable(experts)
+        return experts, weights
+
+    @staticmethod
+    def backward(ctx, _d_experts, d_weights):
+        experts, weights = ctx.saved_tensors
+        return ops.router_topk_bwd(experts, weights, d_weights.contiguous(), ctx.num_experts), None, None, None
+
+
+def route_and_schedule(workspace: MoKWorkspace, config: MoKConfig, logits: torch.Tensor, *,
+                       num_local_experts: int) -> tuple[MoKSchedule, torch.Tensor, torch.Tensor]:
+    """route() + build_schedule() with the int32 routes written straight into every rank's all-gather buffer by the
+    router kernel (no cast, no separate all-gather launch).  Returns (schedule, top_experts, router_weights)."""
+    if not isinstance(workspace, MoKWorkspace):
+        raise TypeError("workspace must be a MoKWorkspace")
+    if not isinstance(config, MoKConfig):
+        raise TypeError("config must be a MoKConfig")
+    _validate_config(config, workspace)
+    if type(num_local_experts) is not int or num_local_experts <= 0:
+        raise ValueError("num_local_experts must be a positive integer")
+    if logits.ndim != 2 or logits.shape[0] != workspace.num_local_tokens:
+        raise ValueError("logits must have shape (num_local_tokens, num_experts)")
+    if logits.shape[1] != num_local_experts * workspace.ep_size:
+        raise ValueError("logits must have num_local_experts * ep_size columns")
+    top_experts, router_weights = _RouteGather.apply(logits, workspace.topk, workspace.all_gather_top_experts_buffer,
+                                                     workspace.ep_rank)
+    if workspace.ep_size > 1:
+        _barrier(workspace)
+    peer_rank, peer_token_idx, num_tokens, tokens_per_expert = ops.schedule(
+        workspace.all_gather_top_experts_buffer, num_local_experts, workspace.schedule_capacity, workspace.ep_rank)
+    sched = MoKSchedule(peer_rank=peer_rank, peer_token_idx=peer_token_idx, num_tokens=num_tokens,
+                        tokens_per_expert=tokens_per_expert)
+    return sched, top_experts, router_weights
+
+
 def validate_inputs(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x: torch.Tensor,
                     router_weights: torch.Tensor, grad_output: torch.Tensor | None = None) -> None:
     if not isinstance(config, MoKConfig):

@@ -708,3 +708,87 @@ def dispatch_mlp_swiglu_combine_bwd_mxfp8(
     return (d_x_shared, d_x_routed, d_gate_shared, d_gate_q, d_gate_sc, d_up_shared, d_up_q, d_up_sc,
             d_hidden_shared, d_hidden_routed, d_y_q, d_y_sc, d_w_shared_gate, d_w_routed_gate, d_w_shared_up,
             d_w_routed_up, d_w_shared_down, d_w_routed_down)
+
+
+
+# ------------------------------------------------------------------------------------------
+# router in front of the layer (no reference op: the reference takes finished routes; the law is the
+# one its tests use, torch.topk on the logits + softmax over the K values, tests/utils.py:82-84)
+# ------------------------------------------------------------------------------------------
+def _router_args(logits: Tensor, topk: int) -> tuple[int, int]:
+    _need(logits.is_cuda and logits.ndim == 2 and logits.is_contiguous(),
+          "logits must be a contiguous CUDA tensor of shape (num_local_tokens, num_experts)")
+    _need(logits.dtype == torch.float32, "logits must have dtype torch.float32", TypeError)
+    T, E = logits.shape
+    _need(T > 0 and 0 < E <= 1024, "num_experts must be in [1, 1024]")
+    _need(type(topk) is int and 0 < topk <= min(32, E), "topk must be in [1, min(32, num_experts)]")
+    return T, E
+
+
+@torch.library.custom_op("mok::router_topk", mutates_args=())
+def router_topk(logits: Tensor, topk: int) -> tuple[Tensor, Tensor]:
+    """(top_experts int64 [T, K], router_weights f32 [T, K]): the K largest logits of every token in
+    descending order and the softmax over them."""
+    T, E = _router_args(logits, topk)
+    experts = torch.empty(T, topk, dtype=torch.int64, device=logits.device)
+    weights = torch.empty(T, topk, dtype=torch.float32, device=logits.device)
+    _lib.check(_lib.mok_router_topk(logits.data_ptr(), T, E, topk, None, experts.data_ptr(), weights.data_ptr(), None, 0, 0,
+                                    _lib.stream_ptr(logits.device)), "router_topk")
+    return experts, weights
+
+
+@torch.library.custom_op("mok::router_topk_gather", mutates_args=("all_gather_top_experts_buffer",))
+def router_topk_gather(logits: Tensor, topk: int, all_gather_top_experts_buffer: Tensor, rank: int) -> tuple[Tensor, Tensor]:
+    """router_topk that also writes the int32 routes into slot `rank` of every rank's all-gather buffer
+    (what the cast + all_gather_top_experts of build_schedule would do)."""
+    T, E = _router_args(logits, topk)
+    buf = all_gather_top_experts_buffer
+    _need(buf.is_cuda and buf.dtype == torch.int32 and buf.is_contiguous() and buf.ndim == 3 and buf.device == logits.device,
+          "all_gather_top_experts_buffer must be a contiguous CUDA int32 tensor (ep_size, num_local_tokens, topk)")
+    ep_size = buf.shape[0]
+    _need(ep_size in _EP_SIZES, f"all_gather_top_experts_buffer ep_size must be one of {_EP_TEXT}")
+    _need(tuple(buf.shape[1:]) == (T, topk), "all_gather_top_experts_buffer must match (num_local_tokens, topk)")
+    _need(type(rank) is int and 0 <= rank < ep_size, "rank must be an integer in [0, ep_size)")
+    peers = _lib.all_gather_peers(buf.data_ptr())
+    if peers is None:
+        _need(ep_size == 1, "all_gather_top_experts_buffer has no registered peer addresses; create it through "
+                            "mok.functional.create_workspace", RuntimeError)
+        peers = [buf.data_ptr()]
+    experts = torch.empty(T, topk, dtype=torch.int64, device=logits.device)
+    weights = torch.empty(T, topk, dtype=torch.float32, device=logits.device)
+    _lib.check(_lib.mok_router_topk(logits.data_ptr(), T, E, topk, None, experts.data_ptr(), weights.data_ptr(),
+                                    _lib.ptr_array(peers), ep_size, rank, _lib.stream_ptr(logits.device)), "router_topk_gather")
+    return experts, weights
+
+
+@torch.library.custom_op("mok::router_topk_bwd", mutates_args=())
+def router_topk_bwd(top_experts: Tensor, router_weights: Tensor, d_router_weights: Tensor, num_experts: int) -> Tensor:
+    """d_logits f32 [T, num_experts] from the gradient of the router weights."""
+    _need(top_experts.is_cuda and top_experts.ndim == 2 and top_experts.dtype in (torch.int64, torch.int32),
+          "top_experts must be a CUDA integer tensor of shape (num_local_tokens, topk)")
+    T, K = top_experts.shape
+    for name, t in (("router_weights", router_weights), ("d_router_weights", d_router_weights)):
+        _need(t.device == top_experts.device and tuple(t.shape) == (T, K), f"{name} must match top_experts")
+        _need(t.dtype == torch.float32, f"{name} must have dtype torch.float32", TypeError)
+    _need(type(num_experts) is int and K <= num_experts <= 1024 and K <= 32, "num_experts must be in [topk, 1024]")
+    idx = top_experts.to(torch.int32).contiguous()
+    d_logits = torch.empty(T, num_experts, dtype=torch.float32, device=top_experts.device)
+    _lib.check(_lib.mok_router_topk_bwd(idx.data_ptr(), router_weights.contiguous().data_ptr(),
+                                        d_router_weights.contiguous().data_ptr(), d_logits.data_ptr(), T, num_experts, K,
+                                        _lib.stream_ptr(top_experts.device)), "router_topk_bwd")
+    return d_logits
+
+
+def _router_setup(ctx, inputs, output):
+    ctx.num_experts = inputs[0].shape[1]
+    ctx.save_for_backward(output[0], output[1])
+    ctx.set_materialize_grads(False)
+
+
+def _router_backward(ctx, _d_experts, d_weights):
+    experts, weights = ctx.saved_tensors
+    d_logits = None if d_weights is None else router_topk_bwd(experts, weights, d_weights.contiguous(), ctx.num_experts)
+    return (d_logits,) + (None,) * (len(ctx.needs_input_grad) - 1)
+
+
+torch.library.register_autograd("mok::router_topk", _router_backward, setup_context=_router_setup)

@@ -16,6 +16,7 @@ Reference anchors (paths are relative to the reference project root):
   MXFP8 quantiser          csrc/mxfp8.cuh:45-72,184, tests/utils.py:179-221
   SwiGLU (+clamp), grads   csrc/mok_megakernel.cuh:612-647,746-776, tests/utils.py:224-235
   epilogues                csrc/utils.cuh:65-117,158-194, tests/utils.py:299-317
+  router (top-K, weights)  tests/utils.py:82-84 (torch.topk on the logits, softmax over the K values)
   layer forward/backward   tests/utils.py:238-296,320-430 and the device rounding
                            points csrc/mok_megakernel.cuh:464-467,776,958,1002,1135
 """
@@ -214,6 +215,28 @@ def mxfp8_dequantize(q: np.ndarray, sc_layout: np.ndarray) -> np.ndarray:
 # --------------------------------------------------------------------------------------
 # SwiGLU and epilogues (torch, fp32)
 # --------------------------------------------------------------------------------------
+def router_topk(logits: np.ndarray, topk: int):
+    """Routes of every token: the K largest logits in descending order (lower expert index first
+    among equal values) and the softmax over those K values, in float64 then rounded to float32.
+    Follows tests/utils.py:82-84."""
+    logits = np.asarray(logits, dtype=np.float32)
+    order = np.argsort(-logits.astype(np.float64), axis=1, kind="stable")[:, :topk]
+    vals = np.take_along_axis(logits, order, axis=1).astype(np.float64)
+    ex = np.exp(vals - vals[:, :1])
+    return order.astype(np.int64), (ex / ex.sum(axis=1, keepdims=True)).astype(np.float32)
+
+
+def router_topk_bwd(experts: np.ndarray, weights: np.ndarray, d_weights: np.ndarray, num_experts: int) -> np.ndarray:
+    """Gradient of router_topk's weights with respect to the logits (softmax Jacobian on the
+    selected experts, zero elsewhere)."""
+    w = weights.astype(np.float64)
+    dw = d_weights.astype(np.float64)
+    inner = (w * dw).sum(axis=1, keepdims=True)
+    d_logits = np.zeros((experts.shape[0], num_experts), dtype=np.float64)
+    np.put_along_axis(d_logits, experts.astype(np.int64), w * (dw - inner), axis=1)
+    return d_logits.astype(np.float32)
+
+
 def swiglu_fwd(gate: torch.Tensor, up: torch.Tensor, limit: float | None) -> torch.Tensor:
     g, u = gate.float(), up.float()
     if limit is not None:

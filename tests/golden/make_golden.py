@@ -2,7 +2,7 @@
 pure-PyTorch test oracles (reference `tests/utils.py`) on the CPU.
 
 Usage (only where the reference tree is mounted):
-    python tests/golden/make_golden.py /path/to/reference
+    python tests/golden/make_golden.py /path/to/reference [router]     (a second word limits the run to that file)
 
 What is stored
   schedule.npz   slot tables from `run_schedule_reference` for a handful of seeded routings,
@@ -11,6 +11,8 @@ What is stored
   layer_w2.npz   the nine results of `run_reference_bf16` on two ranks (gloo), with and
                  without the SwiGLU clamp; inputs come from oracle.make_rank_inputs (seeded),
                  and an input checksum is stored so a drifting RNG is reported as such.
+  router.npz     logits, top-k experts and router weights from the reference's `generate_inputs`
+                 (torch.topk on the logits, softmax over the selected values), two shapes.
   layer_c1.npz   the same for the single-rank CPU configuration T=256, H=512, 8 experts,
                  top-2, I=1024 (seed 0), stored as a strided subsample (every 97th element; arrays of at most 8192
                  elements in full) plus norms.
@@ -122,9 +124,31 @@ def run_layer(ref_root, cfg, limits, port):
     return merged
 
 
-def main(ref_root: str):
+ROUTER_CASES = [dict(T=512, E=64, K=6), dict(T=768, E=256, K=8), dict(T=512, E=8, K=2)]
+
+
+def router_golden(ref) -> None:
+    store = {}
+    for i, c in enumerate(ROUTER_CASES):
+        rank = i
+        out = ref.generate_inputs(rank, torch.device("cpu"), c["E"], c["E"], c["K"], c["T"], 256, 256)
+        # the logits are the generator's first draw (reference tests/utils.py:80-82)
+        g = torch.Generator().manual_seed(1234 + rank)
+        logits = torch.randn(c["T"], c["E"], generator=g)
+        assert torch.equal(torch.topk(logits, c["K"], dim=1).indices, out[1])
+        store[f"{i}/logits"] = logits.numpy()
+        store[f"{i}/topk_experts"] = out[1].numpy()
+        store[f"{i}/router_weights"] = out[2].numpy()
+    np.savez_compressed(os.path.join(HERE, "router.npz"), **store)
+
+
+def main(ref_root: str, only: str | None = None):
     ref = load_reference(ref_root)
     torch.manual_seed(0)
+    router_golden(ref)
+    if only == "router":
+        print("router golden vectors written to", HERE)
+        return
 
     # ---- scheduler
     store = {}
@@ -186,4 +210,4 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference", sys.argv[2] if len(sys.argv) > 2 else None)
