@@ -396,6 +396,111 @@ def cpu_baseline(name, steps=1, sample_tokens=None):
                       f"{'fwd+bwd' if wl['backward'] else 'fwd'}, {sec:.2f} s per step", "seconds_per_step": sec}
 
 
+class TorchMoE:
+    """GPU-side library baseline for the same layer: routes sorted by expert, NCCL all_to_all_single for dispatch and
+    combine, torch._grouped_mm for the expert GEMMs, autograd for the backward (BF16 only).  What a user would write
+    in plain PyTorch; the counterpart of the reference's benchmarks/bench_nccl_torch.py.  Its splits need one host
+    synchronisation per step (all_to_all_single takes Python lists)."""
+
+    def __init__(self, params, topk, world):
+        self.sg, self.su, self.sd, self.rg, self.ru, self.rd = params
+        self.K, self.W, self.El = topk, world, params[3].shape[0]
+
+    def _a2a(self, rows, out_splits, in_splits):
+        if self.W == 1:
+            return rows
+        import torch.distributed.nn.functional as dnn
+        out = rows.new_empty(sum(out_splits), rows.shape[1])
+        return dnn.all_to_all_single(out, rows, out_splits, in_splits)
+
+    def forward(self, x, top_experts, router_weights):
+        T, H = x.shape
+        K, W, El = self.K, self.W, self.El
+        flat = top_experts.flatten()
+        order = torch.argsort(flat, stable=True)                     # routes by expert, hence by destination rank
+        counts = torch.bincount(flat, minlength=W * El)
+        recv_counts = counts
+        if W > 1:
+            recv_counts = torch.empty_like(counts)
+            dist.all_to_all_single(recv_counts, counts)               # [src rank, local expert]
+        send_splits = counts.view(W, El).sum(1).tolist()
+        recv_splits = recv_counts.view(W, El).sum(1).tolist()
+        recv = self._a2a(x[order // K], recv_splits, send_splits)
+        # rows arrive ordered by (source rank, expert): regroup them expert-major for the grouped GEMM
+        ids = torch.repeat_interleave(torch.arange(El, device=x.device).repeat(W), recv_counts)
+        perm = torch.argsort(ids, stable=True)
+        offs = torch.cumsum(recv_counts.view(W, El).sum(0), 0).to(torch.int32)
+        grouped = recv[perm]
+        gate = torch._grouped_mm(grouped, self.rg.transpose(1, 2), offs=offs)
+        up = torch._grouped_mm(grouped, self.ru.transpose(1, 2), offs=offs)
+        y = torch._grouped_mm(torch.nn.functional.silu(gate) * up, self.rd.transpose(1, 2), offs=offs)
+        back = torch.empty_like(y).index_copy(0, perm, y)
+        ret = self._a2a(back, send_splits, recv_splits)
+        flat_out = torch.empty_like(ret).index_copy(0, order, ret)
+        shared = (torch.nn.functional.silu(x @ self.sg.T) * (x @ self.su.T)) @ self.sd.T
+        routed = (router_weights.unsqueeze(-1) * flat_out.view(T, K, H).float()).sum(1)
+        return (shared.float() + routed).to(torch.bfloat16)
+
+
+def run_torch(args, rank, world, local_rank):
+    """--impl torch: the TorchMoE baseline on the GPUs, same workload, inputs and timing rules as the product arm."""
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    name = args.workload if args.workload != "auto" else ("C2" if world == 1 else "C3")
+    wl = dict(WORKLOADS[name])
+    if wl.get("mxfp8"):
+        if rank == 0:
+            print(json.dumps({"impl": "torch", "unavailable": "the PyTorch baseline is BF16 only"}), flush=True)
+        return
+    if args.tokens:
+        wl["T"] = args.tokens
+    T, H, I, K = wl["T"], wl["H"], wl["I"], wl["K"]
+    host, params = make_inputs(wl, rank, world, dev)
+    inp = {k: v.to(dev) for k, v in host.items()}
+    leaves = [p.requires_grad_(wl["backward"]) for p in params]
+    x = inp["x"].requires_grad_(wl["backward"])
+    rw = inp["rw"].requires_grad_(wl["backward"])
+    moe = TorchMoE(leaves, K, world)
+
+    def step():
+        out = moe.forward(x, inp["topk"], rw)
+        if wl["backward"]:
+            return out, torch.autograd.grad(out, [x, rw] + leaves, inp["d_out"])
+        return out, None
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[local_rank])
+        torch.cuda.synchronize()
+
+    steps = args.steps
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        step()
+    b.record()
+    barrier()
+    ms = torch.tensor([a.elapsed_time(b)], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    ms_step = ms.item() / steps
+    if rank == 0:
+        flops = layer_flops(T, K, H, I, wl["backward"])
+        print(json.dumps({
+            "impl": "torch", "metric": METRIC, "value": world * flops / (ms_step * 1e-3) / 1e12, "unit": UNIT,
+            "n_gpus": world, "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"{name}: {wl['desc']}", "ep_size": world,
+                       "note": "library baseline: NCCL all_to_all_single + torch._grouped_mm + autograd; "
+                               "none of this repository's kernels"},
+            "gpu_launches": 0}), flush=True)
+
+
 def run_reference(args, rank, world):
     """The reference arm: the reference's CPU implementation of the path (its pure-PyTorch test
     oracle, restated in oracle/) on the host cores, on a bounded sample per step."""
@@ -422,7 +527,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference", "torch"])
     ap.add_argument("--workload", default="auto", choices=["auto"] + sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=0, help="override tokens per rank (profiling a reduced case)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -435,6 +540,13 @@ def main():
         raise SystemExit("--gpus N with N > 1 must be launched with torch.distributed.run (one rank per GPU)")
     if args.impl == "reference":
         run_reference(args, rank, world)
+        return
+    if args.impl == "torch":
+        try:
+            run_torch(args, rank, world, local_rank)
+        finally:
+            if dist.is_initialized():
+                dist.destroy_process_group()
         return
     try:
         run_ours(args, rank, world, local_rank)

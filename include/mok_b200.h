@@ -199,7 +199,7 @@ typedef struct mok_bwd_bf16_args {
     void *d_y_routed;                                     /* [MB, H] */
     void *d_w_shared_gate, *d_w_shared_up, *d_w_shared_down;
     void *d_w_routed_gate, *d_w_routed_up, *d_w_routed_down;
-    /* scratch: router weights per routed row [MB] f32, router-grad partials [MB, I/256] f32 */
+    /* scratch: router weights per routed row [MB] f32, router-grad partials [MB, I/128] f32 */
     float* router_weights_routed;
     float* d_router_weight_partials;
 } mok_bwd_bf16_args;

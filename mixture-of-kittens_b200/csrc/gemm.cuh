@@ -5,12 +5,13 @@
 //   - one elected thread issues tcgen05.mma (M=128, N=256, K=16 per instruction), fp32
 //     accumulators live in tensor memory, double-buffered (2 x 256 columns) so the epilogue of
 //     tile i overlaps the main loop of tile i+1;
-//   - four epilogue warps read the accumulator with tcgen05.ld and apply the fused epilogue:
+//   - eight epilogue warps (two per TMEM lane quarter, each taking half of the tile's columns) read
+//     the accumulator with tcgen05.ld and apply the fused epilogue:
 //     plain bf16 store (optionally accumulating), SwiGLU forward (gate|up halves of one tile),
 //     or SwiGLU backward with the router-gradient partial sums.
 //
-// Warp roles in a 192-thread CTA: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
-// warps 2..5 = epilogue (TMEM lane quarter = warp id % 4).  One CTA per SM; tiles are assigned
+// Warp roles in a 320-thread CTA: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 2..9 = epilogue (TMEM lane quarter = warp id % 4, column half = (warp id - 2) / 4).  One CTA per SM; tiles are assigned
 // round-robin (tile = blockIdx.x + i * gridDim.x), so results do not depend on timing.
 //
 // Row counts come from device memory (num_tokens / tokens_per_expert): nothing here needs a
@@ -33,7 +34,8 @@ constexpr int kStages = 4;
 constexpr int kABytes = kBlockM * kBlockK * 2;   // 16 KB
 constexpr int kBBytes = kBlockN * kBlockK * 2;   // 32 KB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kGemmThreads = 192;
+constexpr int kEpiSplit = 2;                      // epilogue warps per TMEM lane quarter
+constexpr int kGemmThreads = 64 + 128 * kEpiSplit;
 constexpr int kTmemCols = 512;
 constexpr int kMaxExperts = MOK_MAX_LOCAL_EXPERTS;
 constexpr int kGemmSmemBytes = kStages * kStageBytes + 256 + kMaxExperts * 4 + 1024;   // also 6 x 32 KB stages of the two-CTA form
@@ -64,7 +66,7 @@ struct GemmParams {
     long long out_expert_stride;   // weight-gradient mode: elements between experts in out0
     int accumulate;                // weight-gradient mode: add to the bf16 value already stored
     const float* row_scale;        // swiglu bwd: router weight per routed row (nullptr for the shared expert)
-    float* partials;               // swiglu bwd: [rows, n_tiles] router-gradient partial sums
+    float* partials;               // swiglu bwd: [rows, n_tiles * kEpiSplit] router-gradient partial sums (one per 128 columns)
     float limit;
     int has_limit;
     int* status;
@@ -115,7 +117,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     }
     if (threadIdx.x == 0) {
         for (int s = 0; s < kS; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], k2 ? 8 : 4); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&tfull_bar[b], 1); mbar_init(&tempty_bar[b], (k2 ? 8 : 4) * kEpiSplit); }
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -280,6 +282,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
     } else {
         // ------------------------------------------------------------------ epilogue warps
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;            // which share of the tile's columns this warp handles
         const int r_in_tile = quarter * 32 + lane;
         int it = 0;
         bool ok = true;
@@ -298,7 +301,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                                      row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN;
                 const bool skip_store = kWgrad && p.accumulate && k_blocks == 0;   // adding zero: leave as is
 #pragma unroll 1
-                for (int c = 0; c < (skip_store ? 0 : kBlockN / 32); ++c) {
+                constexpr int kPer = kBlockN / 32 / kEpiSplit;
+                for (int c = half * kPer; c < (skip_store ? 0 : (half + 1) * kPer); ++c) {
                     uint32_t acc[32];
                     if (k_blocks > 0) { tmem_ld_32x32(t_addr + c * 32, acc); tmem_ld_wait(); }
                     else {
@@ -323,7 +327,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
             } else if constexpr (kEpi == kEpiSwigluFwd) {
                 const size_t off = row * p.ld_out + static_cast<size_t>(n_idx) * (kBlockN / 2);
 #pragma unroll 1
-                for (int c = 0; c < kBlockN / 64; ++c) {
+                constexpr int kPer = kBlockN / 64 / kEpiSplit;
+                for (int c = half * kPer; c < (half + 1) * kPer; ++c) {
                     uint32_t g[32], u[32];
                     tmem_ld_32x32(t_addr + c * 32, g);
                     tmem_ld_32x32(t_addr + kBlockN / 2 + c * 32, u);
@@ -357,7 +362,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 if (p.row_scale) { const float w = p.row_scale[row]; inv_w = w > 0.0f ? 1.0f / w : 0.0f; }
                 float partial = 0.0f;
 #pragma unroll 1
-                for (int c = 0; c < kBlockN / 32; ++c) {
+                constexpr int kPer = kBlockN / 32 / kEpiSplit;
+                for (int c = half * kPer; c < (half + 1) * kPer; ++c) {
                     uint32_t acc[32];
                     tmem_ld_32x32(t_addr + c * 32, acc);
                     const uint4* sg = reinterpret_cast<const uint4*>(p.in0 + off + c * 32);
@@ -398,7 +404,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                         du[v] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
                     }
                 }
-                if (p.partials) p.partials[row * p.n_tiles + n_idx] = partial;
+                if (p.partials) p.partials[(row * p.n_tiles + n_idx) * kEpiSplit + half] = partial;
             }
             tc_fence_before();
             __syncwarp();

@@ -399,7 +399,7 @@ extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
     if (!a->router_weights_routed || !a->d_router_weight_partials) return MOK_ERR_INVALID;
     const void* dy_local = dy_peers.p[d.rank];
     const void* x_local = x_peers.p[d.rank];
-    const int partial_cols = d.I / kBlockN;
+    const int partial_cols = d.I / kBlockN * kEpiSplit;
     Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
     MOK_TRY(pipe.error());
     MOK_TRY(pipe.fork());

@@ -390,7 +390,7 @@ def dispatch_mlp_swiglu_combine_bwd_bf16(
     d_w_routed_gate, d_w_routed_up = torch.empty(El, I, H, **bf), torch.empty(El, I, H, **bf)
     d_w_routed_down = torch.empty(El, H, I, **bf)
     row_weights = torch.empty(MB, dtype=torch.float32, device=dev)
-    partials = torch.empty(MB, I // 256, dtype=torch.float32, device=dev)
+    partials = torch.empty(MB, I // 128, dtype=torch.float32, device=dev)
 
     a = _lib.BwdBf16Args()
     a.c = _common(x, ep_size, I, El, topk, cap, MB, minibatch_size, num_comm_sms, swiglu_limit,

@@ -88,6 +88,36 @@ def main():
                 failures.append(f"case {ci}: {name} rel-L2 {e:.3e}")
         if not torch.equal(outs[0][0], outs[1][0]) or any(not torch.equal(a, b) for a, b in zip(outs[0][1], outs[1][1])):
             failures.append(f"case {ci}: two runs differ bitwise")
+    # router kernel writing the routes straight into every rank's all-gather buffer == cast + all-gather, and the
+    # plain-PyTorch baseline (all_to_all_single + grouped_mm) computes the same layer as the kernels
+    import bench
+    c = cases[1]
+    El = c["E"] // world
+    me = O.make_rank_inputs(rank, T=c["T"], H=c["H"], I=c["I"], E=c["E"], W=world, K=c["K"], seed=77)
+    cfg = F.MoKConfig(minibatch_size=256, macrobatch_size=c["macro"], schedule_capacity_multiplier=1.0,
+                      all_gather_top_experts_chunk_bytes=16)
+    ws = F.get_workspace(cfg, dist.group.WORLD, device=dev, num_local_tokens=c["T"], hidden_size=c["H"], topk=c["K"])
+    w = [t.to(dev) for t in (me.w_shared_gate, me.w_shared_up, me.w_shared_down, me.w_routed_gate, me.w_routed_up,
+                             me.w_routed_down)]
+    x = me.x.to(dev)
+    logits = torch.randn(c["T"], c["E"], generator=torch.Generator().manual_seed(900 + rank)).to(dev)
+    sched_a, experts, weights = F.route_and_schedule(ws, cfg, logits, num_local_experts=El)
+    sched_b = F.build_schedule(ws, cfg, experts, num_local_experts=El)
+    n = int(sched_b.num_tokens.item())
+    valid = sched_b.peer_rank[:n] >= 0
+    same = (torch.equal(sched_a.num_tokens, sched_b.num_tokens) and torch.equal(sched_a.tokens_per_expert, sched_b.tokens_per_expert)
+            and torch.equal(sched_a.peer_rank[:n], sched_b.peer_rank[:n])
+            and torch.equal(sched_a.peer_token_idx[:n][valid], sched_b.peer_token_idx[:n][valid]))
+    if not same:
+        failures.append("route_and_schedule tables differ from build_schedule")
+    out, _ = F.forward(cfg, ws, sched_b, x, weights, *w)
+    out_t = bench.TorchMoE(w, c["K"], world).forward(x, experts, weights)
+    e = rel(out_t.float(), out.float())
+    worst = max(worst, e)
+    if e > 1e-2:
+        failures.append(f"torch baseline vs kernels: output rel-L2 {e:.3e}")
+    if mok.last_status(dev)[0] != 0:
+        failures.append(f"router/baseline section: status {mok.last_status(dev)}")
     flag = torch.tensor([len(failures)], device=dev)
     dist.all_reduce(flag)
     print(json.dumps({"rank": rank, "world": world, "worst_rel_l2": worst, "failures": failures}), flush=True)
