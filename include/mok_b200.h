@@ -40,6 +40,9 @@ extern "C" {
 
 int mok_version(void);
 const char* mok_error_string(int code);
+/* Name, text and source position of the last CUDA runtime call that failed inside this library on the calling
+ * host thread ("" if none): the detail behind a MOK_ERR_CUDA return.  No reference counterpart. */
+const char* mok_last_cuda_error(void);
 
 /* All-gather of the int32 top-k expert ids: rank `rank` stores its `numel` ids into slot `rank`
  * of every peer's [ep_size, numel] buffer with plain peer stores over NVLink.

@@ -435,14 +435,10 @@ int launch_dispatch_rows(const RowMoveParams& p, bool scale, int num_blocks, cud
     ProfScope prof(kSlotDispatch, stream);
     if (scale) return launch_move<kMoveDispatchScale>(p, num_blocks, stream);
     return launch_move<kMoveDispatch>(p, num_blocks, stream);
-    MOK_CUDA_CHECK(cudaGetLastError());
-    return MOK_OK;
 }
 int launch_combine_rows(const RowMoveParams& p, int num_blocks, cudaStream_t stream) {
     ProfScope prof(kSlotCombine, stream);
     return launch_move<kMoveCombine>(p, num_blocks, stream);
-    MOK_CUDA_CHECK(cudaGetLastError());
-    return MOK_OK;
 }
 
 }  // namespace mok

@@ -191,6 +191,19 @@ __device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, u
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+__device__ __forceinline__ void umma_mxf8_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t tmem_sfa, uint32_t tmem_sfb, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(tmem_sfa), "r"(tmem_sfb), "r"(accumulate)
+        : "memory");
+}
+// scale-factor block from each CTA's own shared memory (same offset) into each CTA's own tensor memory
+__device__ __forceinline__ void tmem_cp_32x128b_warpx4_pair(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
 // arrive on the barrier at this offset in both CTAs of the pair once the issued MMAs have completed
 __device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
     const uint16_t mask = 3;
@@ -276,10 +289,16 @@ __device__ __forceinline__ void chunk_range(int win_rows, const ChunkSpec& c, in
 }
 
 #define MOK_TRY(expr) do { int rc__ = (expr); if (rc__ != MOK_OK) return rc__; } while (0)
+// where the last failed CUDA call of this host thread was made (read through mok_last_cuda_error)
+void note_cuda_error(cudaError_t err, const char* file, int line);
+void note_error_text(const char* text);
 #define MOK_CUDA_CHECK(expr)                                       \
     do {                                                           \
         cudaError_t err__ = (expr);                                \
-        if (err__ != cudaSuccess) return MOK_ERR_CUDA;             \
+        if (err__ != cudaSuccess) {                                \
+            ::mok::note_cuda_error(err__, __FILE__, __LINE__);     \
+            return MOK_ERR_CUDA;                                   \
+        }                                                          \
     } while (0)
 
 }  // namespace mok

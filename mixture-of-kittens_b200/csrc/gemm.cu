@@ -2,6 +2,7 @@
 // plain-GEMM entry point used by the tests.
 #include "gemm.cuh"
 
+#include <cstdio>
 #include <cstdlib>
 #include <mutex>
 
@@ -29,15 +30,28 @@ EncodeTiledFn encode_tiled_fn() {
 int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                  uint32_t box_inner, uint32_t box_outer, int elem_bytes) {
     EncodeTiledFn fn = encode_tiled_fn();
-    if (!fn) return MOK_ERR_CUDA;
+    if (!fn) { note_error_text("cuTensorMapEncodeTiled is not available from the driver"); return MOK_ERR_CUDA; }
+    // The encoder is a driver call and needs a context current on the calling thread.  A thread that has made no
+    // context-binding runtime call yet (PyTorch's autograd worker on device 0, served from the caching allocator)
+    // has none, so bind the runtime's primary context once per thread.
+    static thread_local bool context_bound = false;
+    if (!context_bound) { MOK_CUDA_CHECK(cudaFree(nullptr)); context_bound = true; }
     const cuuint64_t dims[2] = {inner, outer};
     const cuuint64_t strides[1] = {row_stride_bytes};
     const cuuint32_t box[2] = {box_inner, box_outer};
     const cuuint32_t estr[2] = {1, 1};
-    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : elem_bytes == 4 ? CU_TENSOR_MAP_DATA_TYPE_UINT32 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+    const CUtensorMapSwizzle sw = elem_bytes == 4 ? CU_TENSOR_MAP_SWIZZLE_NONE : CU_TENSOR_MAP_SWIZZLE_128B;
     const CUresult r = fn(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? MOK_OK : MOK_ERR_CUDA;
+                          sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r == CUDA_SUCCESS) return MOK_OK;
+    char text[224];
+    snprintf(text, sizeof(text), "cuTensorMapEncodeTiled -> %d (base %p, extents %llu x %llu, row stride %llu B, box %u x %u, %d-byte elements)",
+             static_cast<int>(r), base, static_cast<unsigned long long>(inner), static_cast<unsigned long long>(outer),
+             static_cast<unsigned long long>(row_stride_bytes), box_inner, box_outer, elem_bytes);
+    note_error_text(text);
+    return MOK_ERR_CUDA;
 }
 
 int device_sm_count() {
@@ -83,12 +97,13 @@ int launch_inst(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorMap&
     return MOK_OK;
 }
 
+}  // namespace
+
 // two-CTA tiles (256 rows per CTA pair) unless MOK_B200_2CTA=0
 bool use_pairs() {
     static const bool on = [] { const char* e = std::getenv("MOK_B200_2CTA"); return !(e && e[0] == '0'); }();
     return on;
 }
-}  // namespace
 
 int launch_grouped_gemm(int a_major, int b_major, int epi, bool wgrad, const GemmOperands& ops, const GemmParams& p,
                         int max_tiles, int max_ctas, int prof_slot, cudaStream_t stream) {

@@ -300,8 +300,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 __nv_bfloat16* dst = p.out0 + (kWgrad ? static_cast<size_t>(expert) * p.out_expert_stride : 0) +
                                      row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN;
                 const bool skip_store = kWgrad && p.accumulate && k_blocks == 0;   // adding zero: leave as is
-#pragma unroll 1
                 constexpr int kPer = kBlockN / 32 / kEpiSplit;
+#pragma unroll 1
                 for (int c = half * kPer; c < (skip_store ? 0 : (half + 1) * kPer); ++c) {
                     uint32_t acc[32];
                     if (k_blocks > 0) { tmem_ld_32x32(t_addr + c * 32, acc); tmem_ld_wait(); }
@@ -326,8 +326,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 }
             } else if constexpr (kEpi == kEpiSwigluFwd) {
                 const size_t off = row * p.ld_out + static_cast<size_t>(n_idx) * (kBlockN / 2);
-#pragma unroll 1
                 constexpr int kPer = kBlockN / 64 / kEpiSplit;
+#pragma unroll 1
                 for (int c = half * kPer; c < (half + 1) * kPer; ++c) {
                     uint32_t g[32], u[32];
                     tmem_ld_32x32(t_addr + c * 32, g);
@@ -361,8 +361,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 float inv_w = 0.0f;
                 if (p.row_scale) { const float w = p.row_scale[row]; inv_w = w > 0.0f ? 1.0f / w : 0.0f; }
                 float partial = 0.0f;
-#pragma unroll 1
                 constexpr int kPer = kBlockN / 32 / kEpiSplit;
+#pragma unroll 1
                 for (int c = half * kPer; c < (half + 1) * kPer; ++c) {
                     uint32_t acc[32];
                     tmem_ld_32x32(t_addr + c * 32, acc);
@@ -421,9 +421,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
 }
 
 // host side ---------------------------------------------------------------------------------
+// elem_bytes 1 or 2: 128-byte-swizzled operand tiles; elem_bytes 4: unswizzled rows of 32-bit words (scale tiles)
 int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                  uint32_t box_inner, uint32_t box_outer, int elem_bytes);
 int device_sm_count();
+bool use_pairs();
 
 struct GemmOperands {
     const void* a0; const void* b0; const void* a1; const void* b1;   // a1/b1: second segment or "up" weights

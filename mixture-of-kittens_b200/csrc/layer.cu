@@ -227,7 +227,7 @@ class Pipeline {
 public:
     Pipeline(cudaStream_t main, int chunks, int min_rows) : main_(main), chunks_(chunks), min_rows_(min_rows) {
         int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { rc_ = MOK_ERR_CUDA; return; }
+        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { note_error_text("cudaGetDevice failed or device index >= 64"); rc_ = MOK_ERR_CUDA; return; }
         ds_ = &g_streams[dev];
         std::lock_guard<std::mutex> lock(g_streams_mu);
         if (chunks_ > 1 && ds_->side == nullptr) {

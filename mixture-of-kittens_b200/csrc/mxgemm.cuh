@@ -5,8 +5,14 @@
 // contraction runs over tokens), so one shared-memory layout serves every GEMM of the layer:
 //   A tile 128 rows x 128 B, B tile 256 rows x 128 B, 128-byte swizzle, loaded by TMA;
 //   scale tiles (512 B per 128 rows x 128 K, already in the tcgen05 [32][16] layout in global
-//   memory) are fetched with cp.async.bulk and copied shared -> tensor memory by tcgen05.cp
-//   (32x128b, replicated over the four lane quarters) right before the four K=32 MMAs of a stage.
+//   memory) are fetched by TMA through an unswizzled [tiles, 512 B] tensor map and copied shared ->
+//   tensor memory by tcgen05.cp (32x128b, replicated over the four lane quarters) right before the
+//   four K=32 MMAs of a stage.
+// Two-CTA form (k2, the default): a pair of CTAs on neighbouring SMs shares one 256 x 256 tile
+// (tcgen05.mma.cta_group::2).  Each CTA stages its own 128 rows of A with their scales, 128 of the
+// tile's 256 B rows, and the scales of all 256 B rows (every CTA's tensor memory needs them), so a
+// stage is 33.5 KB instead of 49.5 KB and the shared-memory fill per flop drops by a third.  The
+// leader CTA issues tcgen05.cp and tcgen05.mma for both; loads are plain (no cluster multicast).
 // Tensor memory: accumulator columns [0,256), A scales [256,260), B scales [260,268).  There is
 // no room for a second 256-column accumulator beside the scales, so the epilogue warps first pull
 // the whole accumulator into registers as packed bf16 (the layer rounds GEMM outputs to bf16
@@ -35,14 +41,16 @@ constexpr int kMxABytes = kBlockM * kMxBlockK;        // 16 KB
 constexpr int kMxBBytes = kBlockN * kMxBlockK;        // 32 KB
 constexpr int kMxTileBytes = kMxABytes + kMxBBytes;
 constexpr int kMxSfBytes = 512 + 1024;                // A scales + B scales per stage
-// pipeline depth: 4 stages for the plain-store epilogue, 3 where the epilogue needs transpose tiles in shared memory
-__host__ __device__ constexpr int mx_stages(int epi) { return epi == 0 ? 4 : 3; }
+// pipeline depth: one-CTA 4 stages of 49.5 KB for the plain-store epilogue, 3 where the epilogue needs transpose
+// tiles in shared memory; two-CTA 6 and 5 stages of 33.5 KB
+__host__ __device__ constexpr int mx_stages(int epi, bool k2) { return k2 ? (epi == 0 ? 6 : 5) : (epi == 0 ? 4 : 3); }
+__host__ __device__ constexpr int mx_tile_bytes(bool k2) { return kMxABytes + (k2 ? kMxBBytes / 2 : kMxBBytes); }
 constexpr int kMxEpiGroups = 4;                       // epilogue warps per TMEM lane quarter (each takes 64 of the 256 columns)
 constexpr int kMxEpiWarps = 4 * kMxEpiGroups;
 constexpr int kMxThreads = 64 + 32 * kMxEpiWarps;     // producer warp, MMA warp, sixteen epilogue warps
 constexpr int kMxTrBytes = kMxEpiWarps * 32 * 17 * 4; // per-epilogue-warp transpose tiles
-__host__ __device__ constexpr int mx_smem_bytes(int epi) {
-    return mx_stages(epi) * (kMxTileBytes + kMxSfBytes) + 256 + kMaxExperts * 4 + (epi == 0 ? 0 : kMxTrBytes) + 1024;
+__host__ __device__ constexpr int mx_smem_bytes(int epi, bool k2) {
+    return mx_stages(epi, k2) * (mx_tile_bytes(k2) + kMxSfBytes) + 256 + kMaxExperts * 4 + (epi == 0 ? 0 : kMxTrBytes) + 1024;
 }
 constexpr int kMxAccCols = 256, kMxSfaCol = 256, kMxSfbCol = 260;
 
@@ -55,7 +63,8 @@ struct MxGemmParams {
     ChunkSpec chunk;               // row sub-range of the window this launch covers (not used by weight gradients)
     // tiling
     int n_tiles, m_tiles_w, k_tiles_per_seg, num_segs, b_rows_per_expert;
-    // scales: [row_tiles, k_tiles, 512 B]
+    // scales: [row_tiles, k_tiles, 512 B]; the kernel reads them through the four scale tensor maps the launcher
+    // builds from these pointers
     const uint8_t* sfa0; const uint8_t* sfa1; int sfa_k_tiles;
     const uint8_t* sfb0; const uint8_t* sfb1; int sfb_k_tiles;
     // Store / DgradDown: bf16 output
@@ -77,10 +86,9 @@ struct MxGemmParams {
     int* status;
 };
 
-__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-                 ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
+struct MxScaleMaps {               // unswizzled tensor maps over [tiles, 512 B] scale arrays
+    CUtensorMap sfa0, sfa1, sfb0, sfb1;
+};
 // descriptor of a dense 32 x 16-byte scale block for tcgen05.cp (no swizzle, 8-row groups 128 B apart)
 __device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
     uint64_t d = 0;
@@ -125,15 +133,21 @@ __device__ __forceinline__ void mx_store_transposed(const uint32_t (&w)[16], uin
     sct[mx_scale_offset(col0 + lane, static_cast<int>(row0 >> 5), t_rows >> 7)] = static_cast<uint8_t>(sb);
 }
 
-template <int kEpi, bool kWgrad>
+template <int kEpi, bool kWgrad, bool k2>
 __global__ void __launch_bounds__(kMxThreads, 1)
 mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__ CUtensorMap tmB0,
                const __grid_constant__ CUtensorMap tmA1, const __grid_constant__ CUtensorMap tmB1,
-               const MxGemmParams p) {
-    constexpr int kMxStages = mx_stages(kEpi);
+               const __grid_constant__ MxScaleMaps sfm, const MxGemmParams p) {
+    constexpr int kMxStages = mx_stages(kEpi, k2);
+    constexpr int kTile = mx_tile_bytes(k2);
+    constexpr int kTileM = k2 ? 2 * kBlockM : kBlockM;
+    const uint32_t cta_rank = k2 ? cluster_cta_rank() : 0u;
+    const bool leader = cta_rank == 0;
+    const int tile_first = k2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+    const int tile_step = k2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-    uint8_t* sf_smem = smem + kMxStages * kMxTileBytes;
+    uint8_t* sf_smem = smem + kMxStages * kTile;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(sf_smem + kMxStages * kMxSfBytes);
     uint64_t* empty_bar = full_bar + kMxStages;
     uint64_t* tfull_bar = empty_bar + kMxStages;
@@ -151,7 +165,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     if (threadIdx.x == 0) {
         for (int s = 0; s < kMxStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         mbar_init(tfull_bar, 1);
-        mbar_init(tempty_bar, kMxEpiWarps);
+        mbar_init(tempty_bar, k2 ? 2 * kMxEpiWarps : kMxEpiWarps);   // the leader's copy collects both CTAs' warps
         *abort_flag = 0;
         mbar_fence_init();
     }
@@ -166,9 +180,13 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         int run = incl - sum;
         for (int j = 0; j < per; ++j) { const int e = lane * per + j; if (e < E) { run += s_end[e]; s_end[e] = run; } }
     }
-    if (warp == 1) { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+    if (warp == 1) {
+        if (k2) { tmem_alloc_pair(tmem_slot, kTmemCols); tmem_relinquish_pair(); }
+        else { tmem_alloc(tmem_slot, kTmemCols); tmem_relinquish(); }
+    }
     tc_fence_before();
     __syncthreads();
+    if (k2) cluster_sync_all();        // the partner's barriers are initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -176,13 +194,14 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     const int win_rows = max(0, min(n_total - p.row_offset, p.row_limit));
     int chunk_lo = 0, chunk_hi = win_rows;
     if (!kWgrad) chunk_range(win_rows, p.chunk, chunk_lo, chunk_hi);
-    const int m_tile0 = chunk_lo / kBlockM;
-    const int num_tiles = kWgrad ? ((p.accumulate && win_rows == 0) ? 0 : E * p.m_tiles_w * p.n_tiles)
-                                 : ((chunk_hi - chunk_lo) / kBlockM) * p.n_tiles;
+    const int m_tile0 = chunk_lo / kTileM;
+    const int m_tiles_w = k2 ? p.m_tiles_w >> 1 : p.m_tiles_w;
+    const int num_tiles = kWgrad ? ((p.accumulate && win_rows == 0) ? 0 : E * m_tiles_w * p.n_tiles)
+                                 : ((chunk_hi - chunk_lo) / kTileM) * p.n_tiles;
 
     auto decode = [&](int tile, int& m_idx, int& n_idx, int& expert, int& k_row0, int& k_tiles) {
         if constexpr (kWgrad) {
-            const int per_e = p.m_tiles_w * p.n_tiles;
+            const int per_e = m_tiles_w * p.n_tiles;
             expert = tile / per_e;
             const int r = tile - expert * per_e;
             m_idx = r / p.n_tiles;
@@ -198,7 +217,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             m_idx = m_tile0 + m_rel;
             expert = 0;
             if (p.tokens_per_expert) {
-                const int g = p.row_offset + m_idx * kBlockM;
+                const int g = p.row_offset + m_idx * kTileM;
                 int lo = 0, hi = E - 1;
                 while (lo < hi) { const int mid = (lo + hi) >> 1; if (s_end[mid] > g) hi = mid; else lo = mid + 1; }
                 expert = lo;
@@ -212,40 +231,56 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
             tma_prefetch_desc(&tmA0); tma_prefetch_desc(&tmB0);
+            tma_prefetch_desc(&sfm.sfa0); tma_prefetch_desc(&sfm.sfb0);
             int stage = 0; uint32_t phase = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step) {
                 int m_idx, n_idx, expert, k_row0, k_tiles;
                 decode(tile, m_idx, n_idx, expert, k_row0, k_tiles);
                 for (int kt = 0; kt < k_tiles; ++kt) {
                     if (!mbar_wait(&empty_bar[stage], phase ^ 1, abort_flag)) { ok = false; break; }
-                    uint8_t* sa = smem + stage * kMxTileBytes;
+                    uint8_t* sa = smem + stage * kTile;
                     uint8_t* sb = sa + kMxABytes;
                     uint8_t* ssfa = sf_smem + stage * kMxSfBytes;
                     uint8_t* ssfb = ssfa + 512;
-                    mbar_arrive_expect_tx(&full_bar[stage], kMxTileBytes + kMxSfBytes);
+                    if (leader) mbar_arrive_expect_tx(&full_bar[stage], (k2 ? 2 : 1) * (kTile + kMxSfBytes));
+                    auto load = [&](void* dst, const CUtensorMap* map, int x, int y) {
+                        if (k2) tma_load_2d_pair(dst, map, &full_bar[stage], x, y);
+                        else tma_load_2d(dst, map, &full_bar[stage], x, y);
+                    };
                     const int seg = (!kWgrad && kt >= p.k_tiles_per_seg) ? 1 : 0;
                     const int kt_seg = kWgrad ? kt : kt - seg * p.k_tiles_per_seg;
                     const int k_tile_abs = (kWgrad ? k_row0 / kMxBlockK : 0) + kt_seg;      // k-tile index in the tensors
                     const CUtensorMap* ma = seg ? &tmA1 : &tmA0;
                     const CUtensorMap* mb = seg ? &tmB1 : &tmB0;
-                    const uint8_t* sfa = seg ? p.sfa1 : p.sfa0;
-                    const uint8_t* sfb = seg ? p.sfb1 : p.sfb0;
-                    tma_load_2d(sa, ma, &full_bar[stage], k_tile_abs * kMxBlockK, m_idx * kBlockM);
-                    bulk_load_1d(ssfa, sfa + (static_cast<size_t>(m_idx) * p.sfa_k_tiles + k_tile_abs) * 512, 512, &full_bar[stage]);
+                    const CUtensorMap* msa = seg ? &sfm.sfa1 : &sfm.sfa0;
+                    const CUtensorMap* msb = seg ? &sfm.sfb1 : &sfm.sfb0;
+                    // A and its scales: this CTA's 128 rows of the tile
+                    const int a_tile = m_idx * (kTileM / kBlockM) + static_cast<int>(cta_rank);
+                    load(sa, ma, k_tile_abs * kMxBlockK, a_tile * kBlockM);
+                    load(ssfa, msa, 0, a_tile * p.sfa_k_tiles + k_tile_abs);
+                    // B: the whole 256 rows (one CTA) or this CTA's 128 (pair); scales of all 256 rows either way
                     if constexpr (kEpi == kMxEpiGateUp) {
                         const int y = expert * p.b_rows_per_expert + n_idx * (kBlockN / 2);
-                        tma_load_2d(sb, &tmB0, &full_bar[stage], k_tile_abs * kMxBlockK, y);
-                        tma_load_2d(sb + kMxBBytes / 2, &tmB1, &full_bar[stage], k_tile_abs * kMxBlockK, y);
-                        const size_t so = (static_cast<size_t>(y >> 7) * p.sfb_k_tiles + k_tile_abs) * 512;
-                        bulk_load_1d(ssfb, p.sfb0 + so, 512, &full_bar[stage]);
-                        bulk_load_1d(ssfb + 512, p.sfb1 + so, 512, &full_bar[stage]);
+                        if (k2) {                           // the leader holds the gate rows, its partner the up rows
+                            load(sb, leader ? &tmB0 : &tmB1, k_tile_abs * kMxBlockK, y);
+                        } else {
+                            load(sb, &tmB0, k_tile_abs * kMxBlockK, y);
+                            load(sb + kMxBBytes / 2, &tmB1, k_tile_abs * kMxBlockK, y);
+                        }
+                        const int so = (y >> 7) * p.sfb_k_tiles + k_tile_abs;
+                        load(ssfb, &sfm.sfb0, 0, so);
+                        load(ssfb + 512, &sfm.sfb1, 0, so);
                     } else {
                         const int y = (kWgrad ? 0 : expert * p.b_rows_per_expert) + n_idx * kBlockN;
-                        tma_load_2d(sb, mb, &full_bar[stage], k_tile_abs * kMxBlockK, y);
-                        const size_t so = (static_cast<size_t>(y >> 7) * p.sfb_k_tiles + k_tile_abs) * 512;
-                        bulk_load_1d(ssfb, sfb + so, 512, &full_bar[stage]);
-                        bulk_load_1d(ssfb + 512, sfb + so + static_cast<size_t>(p.sfb_k_tiles) * 512, 512, &full_bar[stage]);
+                        if (k2) {
+                            load(sb, mb, k_tile_abs * kMxBlockK, y + static_cast<int>(cta_rank) * (kBlockN / 2));
+                        } else {
+                            load(sb, mb, k_tile_abs * kMxBlockK, y);
+                        }
+                        const int so = (y >> 7) * p.sfb_k_tiles + k_tile_abs;
+                        load(ssfb, msb, 0, so);
+                        load(ssfb + 512, msb, 0, so + p.sfb_k_tiles);
                     }
                     if (++stage == kMxStages) { stage = 0; phase ^= 1; }
                 }
@@ -253,12 +288,12 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_mxf8(kBlockM, kBlockN, 0, 0);
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = make_idesc_mxf8(kTileM, kBlockN, 0, 0);
             int stage = 0; uint32_t phase = 0;
             int it = 0;
             bool ok = true;
-            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+            for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++it) {
                 int m_idx, n_idx, expert, k_row0, k_tiles;
                 decode(tile, m_idx, n_idx, expert, k_row0, k_tiles);
                 if (!mbar_wait(tempty_bar, (it & 1) ^ 1, abort_flag)) { ok = false; break; }
@@ -266,26 +301,34 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 for (int kt = 0; kt < k_tiles; ++kt) {
                     if (!mbar_wait(&full_bar[stage], phase, abort_flag)) { ok = false; break; }
                     tc_fence_after();
-                    const uint32_t sa = smem_u32(smem + stage * kMxTileBytes);
+                    const uint32_t sa = smem_u32(smem + stage * kTile);
                     const uint32_t sb = sa + kMxABytes;
                     const uint32_t ssf = smem_u32(sf_smem + stage * kMxSfBytes);
-                    tmem_cp_32x128b_warpx4(tmem_base + kMxSfaCol, make_sf_desc(ssf));
-                    tmem_cp_32x128b_warpx4(tmem_base + kMxSfbCol, make_sf_desc(ssf + 512));
-                    tmem_cp_32x128b_warpx4(tmem_base + kMxSfbCol + 4, make_sf_desc(ssf + 1024));
+                    if (k2) {
+                        tmem_cp_32x128b_warpx4_pair(tmem_base + kMxSfaCol, make_sf_desc(ssf));
+                        tmem_cp_32x128b_warpx4_pair(tmem_base + kMxSfbCol, make_sf_desc(ssf + 512));
+                        tmem_cp_32x128b_warpx4_pair(tmem_base + kMxSfbCol + 4, make_sf_desc(ssf + 1024));
+                    } else {
+                        tmem_cp_32x128b_warpx4(tmem_base + kMxSfaCol, make_sf_desc(ssf));
+                        tmem_cp_32x128b_warpx4(tmem_base + kMxSfbCol, make_sf_desc(ssf + 512));
+                        tmem_cp_32x128b_warpx4(tmem_base + kMxSfbCol + 4, make_sf_desc(ssf + 1024));
+                    }
                     const uint64_t adesc = make_smem_desc(sa, 16, 1024);
                     const uint64_t bdesc = make_smem_desc(sb, 16, 1024);
 #pragma unroll
                     for (int k = 0; k < kMxBlockK / 32; ++k) {
                         const uint32_t id = idesc | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
-                        umma_mxf8(tmem_base, adesc + ((k * 32) >> 4), bdesc + ((k * 32) >> 4), id, tmem_base + kMxSfaCol,
-                                  tmem_base + kMxSfbCol, (kt > 0 || k > 0) ? 1u : 0u);
+                        if (k2) umma_mxf8_pair(tmem_base, adesc + ((k * 32) >> 4), bdesc + ((k * 32) >> 4), id, tmem_base + kMxSfaCol,
+                                               tmem_base + kMxSfbCol, (kt > 0 || k > 0) ? 1u : 0u);
+                        else umma_mxf8(tmem_base, adesc + ((k * 32) >> 4), bdesc + ((k * 32) >> 4), id, tmem_base + kMxSfaCol,
+                                       tmem_base + kMxSfbCol, (kt > 0 || k > 0) ? 1u : 0u);
                     }
-                    umma_commit(&empty_bar[stage]);
+                    if (k2) umma_commit_pair(&empty_bar[stage]); else umma_commit(&empty_bar[stage]);
                     if (++stage == kMxStages) { stage = 0; phase ^= 1; }
                 }
                 if (!ok) break;
-                if (k_tiles > 0) umma_commit(tfull_bar);
-                else mbar_arrive(tfull_bar);
+                if (k_tiles > 0) { if (k2) umma_commit_pair(tfull_bar); else umma_commit(tfull_bar); }
+                else { mbar_arrive(tfull_bar); if (k2) mbar_arrive_cta(tfull_bar, 1); }
             }
         }
     } else {
@@ -299,7 +342,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         uint32_t* tr = tr_smem + (warp - 2) * kMxTrWords;
         int it = 0;
         bool ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++it) {
             int m_idx, n_idx, expert, k_row0, k_tiles;
             decode(tile, m_idx, n_idx, expert, k_row0, k_tiles);
             if (!mbar_wait(tfull_bar, it & 1, abort_flag)) { ok = false; break; }
@@ -321,9 +364,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             }
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(tempty_bar);      // accumulator is free for the next tile
+            if (lane == 0) { if (k2) mbar_arrive_leader(tempty_bar); else mbar_arrive(tempty_bar); }   // accumulator is free
 
-            const size_t row = static_cast<size_t>(m_idx) * kBlockM + r_in_tile;
+            const size_t row = static_cast<size_t>(m_idx) * kTileM + cta_rank * kBlockM + r_in_tile;
             if constexpr (kEpi == kMxEpiStore) {
                 if (!(kWgrad && p.accumulate && k_tiles == 0)) {
                     __nv_bfloat16* dst = p.out_bf16 + (kWgrad ? static_cast<size_t>(expert) * p.out_expert_stride : 0) +
@@ -418,7 +461,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 
     tc_fence_before();
     __syncthreads();
-    if (warp == 1) { tc_fence_after(); tmem_dealloc(tmem_base, kTmemCols); }
+    if (k2) cluster_sync_all();        // neither CTA frees tensor memory or exits while its partner may still signal it
+    if (warp == 1) { tc_fence_after(); if (k2) tmem_dealloc_pair(tmem_base, kTmemCols); else tmem_dealloc(tmem_base, kTmemCols); }
     if (threadIdx.x == 0 && *abort_flag) report_status(p.status, MOK_STATUS_PIPELINE_TIMEOUT, 100 + warp);
 }
 
@@ -427,6 +471,6 @@ struct MxGemmOperands {
     uint64_t a_inner, a_outer, b_inner, b_outer;      // bytes of K per row, rows
 };
 int launch_mx_gemm(int epi, bool wgrad, const MxGemmOperands& ops, const MxGemmParams& p, int max_tiles, int max_ctas,
-                   int prof_slot, cudaStream_t stream);
+                   int prof_slot, cudaStream_t stream, bool allow_pairs = true);
 
 }  // namespace mok

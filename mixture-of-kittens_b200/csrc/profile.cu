@@ -1,6 +1,7 @@
 #include "profile.cuh"
 
 #include <atomic>
+#include <cstdio>
 #include <mutex>
 #include <vector>
 
@@ -83,3 +84,18 @@ extern "C" int mok_profile_collect(double* ms_per_slot, long long* launches_per_
     g_spans.clear();
     return rc;
 }
+
+// ---- description of the last failed CUDA call of the calling host thread -------------------------
+namespace mok {
+namespace {
+thread_local char t_cuda_error[256] = "";
+}
+void note_cuda_error(cudaError_t err, const char* file, int line) {
+    const char* base = file;
+    for (const char* c = file; *c; ++c) if (*c == '/') base = c + 1;
+    snprintf(t_cuda_error, sizeof(t_cuda_error), "%s (%s) at %s:%d", cudaGetErrorName(err), cudaGetErrorString(err), base, line);
+}
+void note_error_text(const char* text) { snprintf(t_cuda_error, sizeof(t_cuda_error), "%s", text); }
+}  // namespace mok
+
+extern "C" const char* mok_last_cuda_error(void) { return mok::t_cuda_error; }

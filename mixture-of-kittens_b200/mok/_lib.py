@@ -119,6 +119,7 @@ def _sig(name, restype, argtypes):
 
 mok_version = _sig("mok_version", C.c_int, [])
 mok_error_string = _sig("mok_error_string", C.c_char_p, [C.c_int])
+mok_last_cuda_error = _sig("mok_last_cuda_error", C.c_char_p, [])
 mok_all_gather_top_experts = _sig("mok_all_gather_top_experts", C.c_int, [vp, C.c_int64, u64p, C.c_int, C.c_int, vp])
 mok_barrier_all = _sig("mok_barrier_all", C.c_int, [vp, u64p, C.c_int, vp, vp, C.c_uint64, vp])
 mok_schedule_scratch_bytes = _sig("mok_schedule_scratch_bytes", C.c_size_t, [C.c_int, C.c_int])
@@ -160,6 +161,9 @@ def check(rc: int, what: str) -> None:
         raise NotImplementedError(f"{what}: {msg}")
     if rc == -4:
         raise ValueError(f"{what}: {msg}")
+    if rc == -2:
+        detail = mok_last_cuda_error().decode()
+        raise MokNativeError(f"{what}: {msg}: {detail}")
     raise MokNativeError(f"{what}: {msg}")
 
 
