@@ -13,8 +13,9 @@
 // tile's 256 B rows, and the scales of all 256 B rows (every CTA's tensor memory needs them), so a
 // stage is 33.5 KB instead of 49.5 KB and the shared-memory fill per flop drops by a third.  The
 // leader CTA issues tcgen05.cp and tcgen05.mma for both; loads are plain (no cluster multicast).
-// Tensor memory: accumulator columns [0,256), A scales [256,260), B scales [260,268).  There is
-// no room for a second 256-column accumulator beside the scales, so the epilogue warps first pull
+// Tensor memory: accumulator columns [0,256), then a ring of four 16-column scale slots (A scales 4
+// columns, B scales 8) used by consecutive k-tiles.  There is no room for a second 256-column
+// accumulator beside the scales, so the epilogue warps first pull
 // the whole accumulator into registers as packed bf16 (the layer rounds GEMM outputs to bf16
 // before any further use anyway), release it, and only then run the fused epilogue — the next
 // tile's main loop overlaps everything but that read-out.
@@ -52,7 +53,8 @@ constexpr int kMxTrBytes = kMxEpiWarps * 32 * 17 * 4; // per-epilogue-warp trans
 __host__ __device__ constexpr int mx_smem_bytes(int epi, bool k2) {
     return mx_stages(epi, k2) * (mx_tile_bytes(k2) + kMxSfBytes) + 256 + kMaxExperts * 4 + (epi == 0 ? 0 : kMxTrBytes) + 1024;
 }
-constexpr int kMxAccCols = 256, kMxSfaCol = 256, kMxSfbCol = 260;
+// tensor-memory columns: accumulator [0,256); then four scale slots of 16 columns (A scales 4, B scales 8, 4 spare)
+constexpr int kMxAccCols = 256, kMxSfaCol = 256, kMxSfSlots = 4, kMxSfSlotCols = 16;
 
 struct MxGemmParams {
     // row domain (same meaning as GemmParams)
@@ -291,6 +293,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         if (lane == 0 && leader) {
             constexpr uint32_t idesc = make_idesc_mxf8(kTileM, kBlockN, 0, 0);
             int stage = 0; uint32_t phase = 0;
+            uint32_t sf_slot = 0;
             int it = 0;
             bool ok = true;
             for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++it) {
@@ -304,24 +307,29 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                     const uint32_t sa = smem_u32(smem + stage * kTile);
                     const uint32_t sb = sa + kMxABytes;
                     const uint32_t ssf = smem_u32(sf_smem + stage * kMxSfBytes);
+                    // the scales of consecutive k-tiles go to different tensor-memory columns, so this copy does not
+                    // have to wait for the previous k-tile's MMAs to finish reading theirs
+                    const uint32_t sfa_t = tmem_base + kMxSfaCol + sf_slot * kMxSfSlotCols;
+                    const uint32_t sfb_t = sfa_t + 4;
+                    sf_slot = (sf_slot + 1) & (kMxSfSlots - 1);
                     if (k2) {
-                        tmem_cp_32x128b_warpx4_pair(tmem_base + kMxSfaCol, make_sf_desc(ssf));
-                        tmem_cp_32x128b_warpx4_pair(tmem_base + kMxSfbCol, make_sf_desc(ssf + 512));
-                        tmem_cp_32x128b_warpx4_pair(tmem_base + kMxSfbCol + 4, make_sf_desc(ssf + 1024));
+                        tmem_cp_32x128b_warpx4_pair(sfa_t, make_sf_desc(ssf));
+                        tmem_cp_32x128b_warpx4_pair(sfb_t, make_sf_desc(ssf + 512));
+                        tmem_cp_32x128b_warpx4_pair(sfb_t + 4, make_sf_desc(ssf + 1024));
                     } else {
-                        tmem_cp_32x128b_warpx4(tmem_base + kMxSfaCol, make_sf_desc(ssf));
-                        tmem_cp_32x128b_warpx4(tmem_base + kMxSfbCol, make_sf_desc(ssf + 512));
-                        tmem_cp_32x128b_warpx4(tmem_base + kMxSfbCol + 4, make_sf_desc(ssf + 1024));
+                        tmem_cp_32x128b_warpx4(sfa_t, make_sf_desc(ssf));
+                        tmem_cp_32x128b_warpx4(sfb_t, make_sf_desc(ssf + 512));
+                        tmem_cp_32x128b_warpx4(sfb_t + 4, make_sf_desc(ssf + 1024));
                     }
                     const uint64_t adesc = make_smem_desc(sa, 16, 1024);
                     const uint64_t bdesc = make_smem_desc(sb, 16, 1024);
 #pragma unroll
                     for (int k = 0; k < kMxBlockK / 32; ++k) {
                         const uint32_t id = idesc | (static_cast<uint32_t>(k) << 29) | (static_cast<uint32_t>(k) << 4);
-                        if (k2) umma_mxf8_pair(tmem_base, adesc + ((k * 32) >> 4), bdesc + ((k * 32) >> 4), id, tmem_base + kMxSfaCol,
-                                               tmem_base + kMxSfbCol, (kt > 0 || k > 0) ? 1u : 0u);
-                        else umma_mxf8(tmem_base, adesc + ((k * 32) >> 4), bdesc + ((k * 32) >> 4), id, tmem_base + kMxSfaCol,
-                                       tmem_base + kMxSfbCol, (kt > 0 || k > 0) ? 1u : 0u);
+                        if (k2) umma_mxf8_pair(tmem_base, adesc + ((k * 32) >> 4), bdesc + ((k * 32) >> 4), id, sfa_t, sfb_t,
+                                               (kt > 0 || k > 0) ? 1u : 0u);
+                        else umma_mxf8(tmem_base, adesc + ((k * 32) >> 4), bdesc + ((k * 32) >> 4), id, sfa_t, sfb_t,
+                                       (kt > 0 || k > 0) ? 1u : 0u);
                     }
                     if (k2) umma_commit_pair(&empty_bar[stage]); else umma_commit(&empty_bar[stage]);
                     if (++stage == kMxStages) { stage = 0; phase ^= 1; }
