@@ -118,3 +118,43 @@ def test_fake_tensor_shapes():
         assert len(bwd) == 15 and tuple(bwd[10].shape) == (El, I, H) and tuple(bwd[14].shape) == (El, H, I)
         assert tuple(ops.fwd_epilogue(bf(T, H), bf(T * K, H), torch.empty(T, K, device=dev)).shape) == (T, H)
         assert tuple(ops.bwd_epilogue(bf(T, H), bf(T * K, H)).shape) == (T, H)
+
+
+def test_added_operators_and_wrappers():
+    """The operators this build adds on top of the reference's ten, their schemas, fake shapes and argument errors."""
+    import mok
+    ops = mok.ops
+    for n in ("router_topk", "router_topk_gather", "router_topk_bwd", "fwd_epilogue_rows"):
+        assert hasattr(torch.ops.mok, n), n
+    def mutated(op):
+        return {a.name for a in op.default._schema.arguments if a.alias_info is not None and a.alias_info.is_write}
+    assert mutated(torch.ops.mok.router_topk) == set()
+    assert mutated(torch.ops.mok.router_topk_gather) == {"all_gather_top_experts_buffer"}
+    assert mutated(torch.ops.mok.fwd_epilogue_rows) == set()
+    # defer_combine is a trailing, defaulted argument of the four layer operators
+    for n in ("dispatch_mlp_swiglu_combine_fwd_bf16", "dispatch_mlp_swiglu_combine_bwd_bf16",
+              "dispatch_mlp_swiglu_combine_fwd_mxfp8", "dispatch_mlp_swiglu_combine_bwd_mxfp8"):
+        last = getattr(torch.ops.mok, n).default._schema.arguments[-1]
+        assert last.name == "defer_combine" and last.default_value is False
+    with pytest.raises(ValueError):
+        ops.router_topk(torch.zeros(512, 64), 6)                                # not a CUDA tensor
+    with pytest.raises(ValueError):
+        ops.router_topk_bwd(torch.zeros(512, 6, dtype=torch.int64), torch.zeros(512, 6), torch.zeros(512, 6), 64)
+    with FakeTensorMode():
+        dev = "cuda"
+        e, w = ops.router_topk(torch.empty(512, 64, device=dev), 6)
+        assert tuple(e.shape) == (512, 6) and e.dtype == torch.int64 and w.dtype == torch.float32
+        e, w = ops.router_topk_gather(torch.empty(512, 64, device=dev), 6,
+                                      torch.empty(4, 512, 6, dtype=torch.int32, device=dev), 1)
+        assert tuple(w.shape) == (512, 6)
+        g = ops.router_topk_bwd(e, w, w, 64)
+        assert tuple(g.shape) == (512, 64) and g.dtype == torch.float32
+        out = ops.fwd_epilogue_rows(torch.empty(512, 256, dtype=torch.bfloat16, device=dev),
+                                    torch.empty(4096, 256, dtype=torch.bfloat16, device=dev),
+                                    torch.empty(4096, dtype=torch.int32, device=dev),
+                                    torch.empty(4096, dtype=torch.int32, device=dev),
+                                    torch.empty(1, dtype=torch.int32, device=dev), torch.empty(512, 2, device=dev))
+        assert tuple(out.shape) == (512, 256) and out.dtype == torch.bfloat16
+    assert mok.ops.SELF_PTRS == [-1]
+    assert callable(mok.nn.moe_experts) and issubclass(mok.nn.MoKLayer, torch.nn.Module)
+    assert callable(mok.functional.route) and callable(mok.functional.route_and_schedule)
