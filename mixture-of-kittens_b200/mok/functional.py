@@ -385,6 +385,14 @@ def validate_inputs(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSch
         raise ValueError("schedule capacity does not match the workspace")
 
 
+def _stage(buffer: torch.Tensor, value: torch.Tensor) -> None:
+    """Copies a per-step input into its rank-visible buffer, unless the caller built it there: passing
+    ``workspace.x_buffer`` / ``d_y_buffer`` / ``router_weight_buffer`` themselves as x / grad_output /
+    router_weights skips the copy (the reference marks these copies as removable, mok/functional.py:513)."""
+    if value is not buffer:
+        buffer.copy_(value)
+
+
 def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x: torch.Tensor,
             router_weights: torch.Tensor, shared_gate_weights: torch.Tensor, shared_up_weights: torch.Tensor,
             shared_down_weights: torch.Tensor,
@@ -406,8 +414,8 @@ def forward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, x
     if local:
         x_buf, x_ptrs, rw_buf = x, ops.SELF_PTRS, router_weights
     else:
-        ws.x_buffer.copy_(x)
-        ws.router_weight_buffer.copy_(router_weights)
+        _stage(ws.x_buffer, x)
+        _stage(ws.router_weight_buffer, router_weights)
         _barrier(ws)
         x_buf, x_ptrs, rw_buf = ws.x_buffer, ws.x_buffer_ptrs, ws.router_weight_buffer
     sched = (schedule.peer_rank, schedule.peer_token_idx, schedule.num_tokens, schedule.tokens_per_expert)
@@ -462,9 +470,9 @@ def backward(config: MoKConfig, workspace: MoKWorkspace, schedule: MoKSchedule, 
         d_y_buf, d_y_ptrs, x_buf, x_ptrs = grad_output, ops.SELF_PTRS, x, ops.SELF_PTRS
         rw_buf, rw_ptrs = router_weights, ops.SELF_PTRS
     else:
-        ws.d_y_buffer.copy_(grad_output)
-        ws.x_buffer.copy_(x)
-        ws.router_weight_buffer.copy_(router_weights)
+        _stage(ws.d_y_buffer, grad_output)
+        _stage(ws.x_buffer, x)
+        _stage(ws.router_weight_buffer, router_weights)
         _barrier(ws)
         d_y_buf, d_y_ptrs, x_buf, x_ptrs = ws.d_y_buffer, ws.d_y_buffer_ptrs, ws.x_buffer, ws.x_buffer_ptrs
         rw_buf, rw_ptrs = ws.router_weight_buffer, ws.router_weight_buffer_ptrs

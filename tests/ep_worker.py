@@ -111,6 +111,12 @@ def main():
     if not same:
         failures.append("route_and_schedule tables differ from build_schedule")
     out, _ = F.forward(cfg, ws, sched_b, x, weights, *w)
+    # inputs built directly in the rank-visible buffers: no staging copy, same bytes out
+    ws.x_buffer.copy_(x)
+    ws.router_weight_buffer.copy_(weights)
+    out_zc, _ = F.forward(cfg, ws, sched_b, ws.x_buffer, ws.router_weight_buffer, *w)
+    if not torch.equal(out, out_zc):
+        failures.append("forward on the workspace buffers differs from forward on copies")
     out_t = bench.TorchMoE(w, c["K"], world).forward(x, experts, weights)
     e = rel(out_t.float(), out.float())
     worst = max(worst, e)
