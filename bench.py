@@ -70,9 +70,9 @@ WORKLOADS = {
 }
 # DRAM bytes per launch of the dominant kernel from the ncu capture summarised under profiles/
 # (filled in per workload once captured; None = not captured)
-# C2: routed gate|up GEMM captured at 2048 tokens (946 MB read + 133 MB written, of which 805 MB are the weights,
-# read once whatever the row count) and scaled by rows to the full launch: 0.805e9 + 147456 rows * 8362 B
-NCU_TRAFFIC_BYTES = {"C2": 2.04e9, "C3": None}
+# C2: routed gate|up GEMM captured at 2048 tokens (951 MB read + 137 MB written, of which 805 MB are the weights,
+# read once whatever the row count) and scaled by rows to the full launch: 0.805e9 + 147456 rows * 8640 B
+NCU_TRAFFIC_BYTES = {"C2": 2.08e9, "C3": None}
 
 
 def layer_flops(T, K, H, I, backward):
