@@ -37,6 +37,15 @@ def test_host_detected_argument_errors():
     assert L.mok_gemm_bf16(ctypes.c_void_p(16), ctypes.c_void_p(16), ctypes.c_void_p(16), 100, 256, 64, 0, 0, None, None) == -1
     assert L.mok_fwd_bf16(None, None) == -1
     assert L.mok_barrier_all(None, None, 4, None, None, 0, None) == -1
+    # entry points without a reference counterpart
+    p16 = ctypes.c_void_p(16)
+    assert L.mok_router_topk(None, 512, 64, 6, None, None, None, None, 0, 0, None) == -1
+    assert L.mok_router_topk(p16, 512, 64, 65, p16, None, p16, None, 0, 0, None) == -1          # topk > 32
+    assert L.mok_router_topk(p16, 512, 2048, 4, p16, None, p16, None, 0, 0, None) == -3         # more than 1024 experts
+    assert L.mok_router_topk_bwd(None, None, None, None, 512, 64, 6, None) == -1
+    assert L.mok_fwd_epilogue_rows(None, None, None, None, None, None, None, None, 512, 256, 2, 4096, None) == -1
+    assert L.mok_bwd_epilogue_rows(None, None, None, 4, None, None, None, None, None, None, 512, 256, 2, 4096, None) == -1
+    assert L.mok_last_cuda_error() == b""
 
 
 def test_struct_sizes_match_header():
