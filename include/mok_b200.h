@@ -146,7 +146,10 @@ int mok_bwd_epilogue_rows(const void* d_x_shared, const void* d_x_routed, const 
 typedef struct mok_layer_common {
     int ep_size, ep_rank;
     int num_local_tokens, hidden, intermediate, num_local_experts, topk;
-    int schedule_capacity, macrobatch_size, minibatch_size, num_comm_sms;
+    int schedule_capacity, macrobatch_size, minibatch_size;
+    int num_comm_sms;                       /* accepted and range-checked by the callers for API compatibility; the row
+                                               movers here are small CTAs that share SMs with the GEMMs, so no SM is
+                                               set aside and the value does not change the launches */
     int has_swiglu_limit;
     float swiglu_limit;
     int defer_combine;                      /* 1: leave the routed results in their rows (y_routed, or d_x_routed and the

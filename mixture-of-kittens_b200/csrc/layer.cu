@@ -236,9 +236,6 @@ public:
             if (cudaStreamCreateWithPriority(&ds_->side, cudaStreamNonBlocking, hi) != cudaSuccess) rc_ = MOK_ERR_CUDA;
         }
     }
-    int chunks() const { return chunks_; }
-    cudaStream_t main() const { return main_; }
-    cudaStream_t side() const { return chunks_ > 1 ? ds_->side : main_; }
     int error() const { return rc_; }
 
     // side stream continues after everything enqueued on main so far / main after side
