@@ -385,7 +385,7 @@ def cpu_baseline(name, steps=1, sample_tokens=None):
     from oracle import mok_oracle as O
     wl = WORKLOADS[name]
     W = 1
-    T = sample_tokens or (4096 if not wl["backward"] else 1024)
+    T = sample_tokens or (min(wl["T"], 16384) if not wl["backward"] else 4096)   # about 3-10 s of CPU work per step
     cfgs = dict(T=T, H=wl["H"], I=wl["I"], E=wl["E"], W=W, K=wl["K"], seed=0, router=wl["router"],
                 with_grad=wl["backward"])
     ranks = [O.make_rank_inputs(r, **cfgs) for r in range(W)]
