@@ -111,6 +111,22 @@ def main():
     if not same:
         failures.append("route_and_schedule tables differ from build_schedule")
     out, _ = F.forward(cfg, ws, sched_b, x, weights, *w)
+    # the nn.Module wrapper (backward runs on the autograd engine's worker thread of this rank's device) gives the
+    # bytes of the functional calls
+    d_out = me.d_output.to(dev)
+    out, ctx = F.forward(cfg, ws, sched_b, x, weights, *w)
+    ref_grads = F.backward(cfg, ws, sched_b, ctx, d_out, x, weights, *w)
+    layer = mok.nn.MoKLayer(c["H"], c["I"], c["E"], c["K"], group=dist.group.WORLD, config=cfg, device=dev, seed=rank)
+    with torch.no_grad():
+        for name, t in zip(("shared_gate", "shared_up", "shared_down", "routed_gate", "routed_up", "routed_down"), w):
+            getattr(layer, name).copy_(t)
+    xg, wg = x.clone().requires_grad_(True), weights.clone().requires_grad_(True)
+    out_l = layer(xg, experts, wg)
+    out_l.backward(d_out)
+    torch.cuda.synchronize()
+    if not (torch.equal(out_l, out) and torch.equal(xg.grad, ref_grads[0]) and torch.equal(wg.grad, ref_grads[1])
+            and torch.equal(layer.routed_down.grad, ref_grads[4]) and torch.equal(layer.shared_gate.grad, ref_grads[5])):
+        failures.append("MoKLayer forward/backward differs from the functional calls")
     # inputs built directly in the rank-visible buffers: no staging copy, same bytes out
     ws.x_buffer.copy_(x)
     ws.router_weight_buffer.copy_(weights)

@@ -150,6 +150,63 @@ def test_full_size_forward_sampled(cuda_device, single_rank_group):
     assert rel_l2(rd(acc), out[idx]) < BF16_REL_L2
 
 
+def test_full_size_backward_sampled(cuda_device, single_rank_group):
+    """One rank's share of BASELINE config 3 at EP=8 with every route local (T=16384, H=4096, 8 experts, top-6,
+    I=1536), forward + backward.  The oracle is too slow for every token, so d_x and d_router_weights of 24 sampled
+    tokens are recomputed in fp32 with the device's bf16 rounding points, and sampled rows of the shared-expert
+    weight gradients are contracted over all tokens from the saved activations."""
+    cfg = dict(T=16384, H=4096, I=1536, E=8, W=1, K=6)
+    inp = O.make_rank_inputs(0, seed=3, **cfg)
+    got = run_layer(cuda_device, single_rank_group, inp, macrobatch=131072, minibatch=4096)
+    rd = lambda t: t.to(torch.bfloat16).float()  # noqa: E731
+    idx = torch.arange(0, cfg["T"], cfg["T"] // 24)[:24]
+    x, d_out = inp.x[idx].float(), inp.d_output[idx].float()
+    # shared expert
+    g, u = rd(x @ inp.w_shared_gate.float().T), rd(x @ inp.w_shared_up.float().T)
+    d_h = rd(d_out @ inp.w_shared_down.float())
+    d_g, d_u, _ = O.swiglu_bwd(g, u, d_h, None)
+    d_x = rd(rd(d_g) @ inp.w_shared_gate.float() + rd(d_u) @ inp.w_shared_up.float())
+    d_rw = torch.zeros(len(idx), cfg["K"])
+    for k in range(cfg["K"]):
+        e = inp.topk_experts[idx, k]
+        w = inp.router_weights[idx, k:k + 1]
+        ge = rd(torch.einsum("th,tih->ti", x, inp.w_routed_gate[e].float()))
+        ue = rd(torch.einsum("th,tih->ti", x, inp.w_routed_up[e].float()))
+        he = rd(O.swiglu_fwd(ge, ue, None))
+        ye = rd(torch.einsum("ti,thi->th", he, inp.w_routed_down[e].float()))
+        d_rw[:, k] = (d_out * ye).sum(-1)
+        d_y = rd(d_out * w)
+        d_he = rd(torch.einsum("th,thi->ti", d_y, inp.w_routed_down[e].float()))
+        d_ge, d_ue, _ = O.swiglu_bwd(ge, ue, d_he, None)
+        d_x = d_x + rd(torch.einsum("ti,tih->th", rd(d_ge), inp.w_routed_gate[e].float())
+                       + torch.einsum("ti,tih->th", rd(d_ue), inp.w_routed_up[e].float()))
+    assert rel_l2(rd(d_x), got["d_x"].cpu().float()[idx]) < BF16_REL_L2
+    assert rel_l2(d_rw, got["d_router_weights"].cpu()[idx]) < BF16_REL_L2
+    # shared-expert weight gradients: sampled rows, contracted over all 16384 tokens on the device in fp32
+    ctx = got["ctx"]
+    dev_d_out = inp.d_output.to(cuda_device).float()
+    rows = torch.arange(0, cfg["H"], cfg["H"] // 8, device=cuda_device)[:8]
+    ref_down = dev_d_out[:, rows].T @ ctx.hidden_shared.float()
+    assert rel_l2(ref_down, got["d_w_shared_down"][rows].float()) < BF16_REL_L2
+    for name in GRAD_NAMES:
+        assert torch.isfinite(got[name].float()).all(), name
+
+
+def test_full_size_mxfp8_share_is_deterministic_and_close_to_bf16(cuda_device, single_rank_group):
+    """A quarter of one rank's share of BASELINE config 4 (H=7168, I=2048, 16 of the 32 local experts, top-8, 4096 tokens):
+    MXFP8 forward + backward twice bit-identically, and within the reference's own MXFP8-vs-BF16 bound
+    (sum|d| / sum|ref| <= 0.1, tests/utils.py:8) of the BF16 run on the same inputs."""
+    cfg = dict(T=4096, H=7168, I=2048, E=16, W=1, K=8)
+    inp = O.make_rank_inputs(0, seed=4, **cfg)
+    a = run_layer(cuda_device, single_rank_group, inp, mxfp8=True, macrobatch=131072, minibatch=4096)
+    b = run_layer(cuda_device, single_rank_group, inp, mxfp8=True, macrobatch=131072, minibatch=4096)
+    ref = run_layer(cuda_device, single_rank_group, inp, macrobatch=131072, minibatch=4096)
+    for name in ("output",) + GRAD_NAMES:
+        assert torch.equal(a[name], b[name]), name
+        r, g = ref[name].float(), a[name].float()
+        assert ((r - g).abs().sum() / r.abs().sum()).item() < 0.1, name
+
+
 # ----------------------------------------------------------------------------------------
 # MXFP8 routed experts
 # ----------------------------------------------------------------------------------------
