@@ -22,7 +22,6 @@ Reference anchors (paths are relative to the reference project root):
 """
 from __future__ import annotations
 
-import math
 from dataclasses import dataclass
 
 import numpy as np
