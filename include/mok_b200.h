@@ -141,7 +141,9 @@ int mok_bwd_epilogue_rows(const void* d_x_shared, const void* d_x_routed, const 
 /* ---- the fused layer passes -------------------------------------------------------------
  * All tensors are row-major and contiguous.  T = num_local_tokens, H = hidden, I = intermediate,
  * El = num_local_experts, K = topk, MB = macrobatch_size, cap = schedule_capacity.  Pointer
- * arrays `*_ptrs` hold ep_size device addresses, one per rank (own rank included). */
+ * arrays `*_ptrs` hold ep_size device addresses, one per rank (own rank included).
+ * Every tensor address must be 32-byte aligned (the kernels use 256-bit accesses and TMA); allocations of the CUDA
+ * runtime and of PyTorch are. */
 
 typedef struct mok_layer_common {
     int ep_size, ep_rank;

@@ -273,6 +273,19 @@ __device__ __forceinline__ float bf16_round(float x) {
     return __bfloat162float(__float2bfloat16_rn(x));
 }
 
+// 256-bit global accesses (sm_100): one instruction moves 32 bytes per lane, so a row-strided epilogue touches the
+// same cache lines with half the load/store instructions of 128-bit accesses.  Addresses must be 32-byte aligned.
+__device__ __forceinline__ void ld_global_256(const void* p, uint32_t (&r)[8]) {
+    asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                 : "l"(p));
+}
+__device__ __forceinline__ void st_global_256(void* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d, uint32_t e, uint32_t f,
+                                              uint32_t g, uint32_t h) {
+    asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                 ::"l"(p), "r"(a), "r"(b), "r"(c), "r"(d), "r"(e), "r"(f), "r"(g), "r"(h) : "memory");
+}
+
 // A window of `win_rows` schedule rows (known only on the device) is cut into `num_chunks` row ranges
 // of equal size, a multiple of 256 and at least `min_rows` (the minibatch size), so that the
 // host can enqueue a fixed number of launches per window and overlap the row movement of one

@@ -108,6 +108,11 @@ bool use_pairs() {
 int launch_grouped_gemm(int a_major, int b_major, int epi, bool wgrad, const GemmOperands& ops, const GemmParams& p,
                         int max_tiles, int max_ctas, int prof_slot, cudaStream_t stream) {
     if (max_tiles <= 0) return MOK_OK;
+    // the epilogues use 256-bit global accesses: 32-byte aligned tensors and row pitches
+    for (const void* ptr : {static_cast<const void*>(p.out0), static_cast<const void*>(p.out1), static_cast<const void*>(p.out2),
+                            static_cast<const void*>(p.in0), static_cast<const void*>(p.in1)})
+        if (reinterpret_cast<uintptr_t>(ptr) % 32 != 0) return MOK_ERR_INVALID;
+    if (p.ld_out % 16 != 0) return MOK_ERR_INVALID;
     CUtensorMap a0, b0, a1, b1;
     // A: K-major box {64 K, 128 rows}; M-major box {64 M, 64 K-rows}
     const uint32_t a_box_outer = a_major == kMajorK ? kBlockM : kBlockK;

@@ -309,19 +309,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
 #pragma unroll
                         for (int i = 0; i < 32; ++i) acc[i] = 0u;
                     }
-                    uint4* d4 = reinterpret_cast<uint4*>(dst + c * 32);
+                    __nv_bfloat16* d16 = dst + c * 32;
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        float f[8];
+                    for (int v = 0; v < 2; ++v) {            // 16 columns = 32 bytes per 256-bit store
+                        float f[16];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) f[i] = __uint_as_float(acc[v * 8 + i]);
+                        for (int i = 0; i < 16; ++i) f[i] = __uint_as_float(acc[v * 16 + i]);
                         if (kWgrad && p.accumulate) {
-                            const uint4 old = d4[v];
-                            const uint32_t o[4] = {old.x, old.y, old.z, old.w};
+                            uint32_t o[8];
+                            ld_global_256(d16 + v * 16, o);
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) { const float2 q = unpack_bf16(o[i]); f[2 * i] += q.x; f[2 * i + 1] += q.y; }
+                            for (int i = 0; i < 8; ++i) { const float2 q = unpack_bf16(o[i]); f[2 * i] += q.x; f[2 * i + 1] += q.y; }
                         }
-                        d4[v] = make_uint4(pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]), pack_bf16(f[6], f[7]));
+                        st_global_256(d16 + v * 16, pack_bf16(f[0], f[1]), pack_bf16(f[2], f[3]), pack_bf16(f[4], f[5]),
+                                      pack_bf16(f[6], f[7]), pack_bf16(f[8], f[9]), pack_bf16(f[10], f[11]),
+                                      pack_bf16(f[12], f[13]), pack_bf16(f[14], f[15]));
                     }
                 }
             } else if constexpr (kEpi == kEpiSwigluFwd) {
@@ -333,16 +335,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                     tmem_ld_32x32(t_addr + c * 32, g);
                     tmem_ld_32x32(t_addr + kBlockN / 2 + c * 32, u);
                     tmem_ld_wait();
-                    uint4* dg = reinterpret_cast<uint4*>(p.out0 + off + c * 32);
-                    uint4* du = reinterpret_cast<uint4*>(p.out1 + off + c * 32);
-                    uint4* dh = reinterpret_cast<uint4*>(p.out2 + off + c * 32);
+                    __nv_bfloat16* dg = p.out0 + off + c * 32;
+                    __nv_bfloat16* du = p.out1 + off + c * 32;
+                    __nv_bfloat16* dh = p.out2 + off + c * 32;
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint32_t gw[4], uw[4], hw[4];
+                    for (int v = 0; v < 2; ++v) {            // 16 columns = 32 bytes per 256-bit store
+                        uint32_t gw[8], uw[8], hw[8];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            gw[i] = pack_bf16(__uint_as_float(g[v * 8 + 2 * i]), __uint_as_float(g[v * 8 + 2 * i + 1]));
-                            uw[i] = pack_bf16(__uint_as_float(u[v * 8 + 2 * i]), __uint_as_float(u[v * 8 + 2 * i + 1]));
+                        for (int i = 0; i < 8; ++i) {
+                            gw[i] = pack_bf16(__uint_as_float(g[v * 16 + 2 * i]), __uint_as_float(g[v * 16 + 2 * i + 1]));
+                            uw[i] = pack_bf16(__uint_as_float(u[v * 16 + 2 * i]), __uint_as_float(u[v * 16 + 2 * i + 1]));
                             float2 gf = unpack_bf16(gw[i]), uf = unpack_bf16(uw[i]);
                             if (p.has_limit) {
                                 gf.x = fminf(gf.x, p.limit); gf.y = fminf(gf.y, p.limit);
@@ -350,9 +352,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                             }
                             hw[i] = pack_bf16(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
                         }
-                        dg[v] = make_uint4(gw[0], gw[1], gw[2], gw[3]);
-                        du[v] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
-                        dh[v] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
+                        st_global_256(dg + v * 16, gw[0], gw[1], gw[2], gw[3], gw[4], gw[5], gw[6], gw[7]);
+                        st_global_256(du + v * 16, uw[0], uw[1], uw[2], uw[3], uw[4], uw[5], uw[6], uw[7]);
+                        st_global_256(dh + v * 16, hw[0], hw[1], hw[2], hw[3], hw[4], hw[5], hw[6], hw[7]);
                     }
                 }
             } else {
@@ -366,25 +368,24 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 for (int c = half * kPer; c < (half + 1) * kPer; ++c) {
                     uint32_t acc[32];
                     tmem_ld_32x32(t_addr + c * 32, acc);
-                    const uint4* sg = reinterpret_cast<const uint4*>(p.in0 + off + c * 32);
-                    const uint4* su = reinterpret_cast<const uint4*>(p.in1 + off + c * 32);
-                    uint4 gv[4], uv[4];
+                    uint32_t gv[2][8], uv[2][8];             // saved gate / up: two 256-bit loads each
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) { gv[v] = sg[v]; uv[v] = su[v]; }
+                    for (int v = 0; v < 2; ++v) {
+                        ld_global_256(p.in0 + off + c * 32 + v * 16, gv[v]);
+                        ld_global_256(p.in1 + off + c * 32 + v * 16, uv[v]);
+                    }
                     tmem_ld_wait();
-                    uint4* dh = reinterpret_cast<uint4*>(p.out0 + off + c * 32);
-                    uint4* dg = reinterpret_cast<uint4*>(p.out1 + off + c * 32);
-                    uint4* du = reinterpret_cast<uint4*>(p.out2 + off + c * 32);
+                    __nv_bfloat16* dh = p.out0 + off + c * 32;
+                    __nv_bfloat16* dg = p.out1 + off + c * 32;
+                    __nv_bfloat16* du = p.out2 + off + c * 32;
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const uint32_t gin[4] = {gv[v].x, gv[v].y, gv[v].z, gv[v].w};
-                        const uint32_t uin[4] = {uv[v].x, uv[v].y, uv[v].z, uv[v].w};
-                        uint32_t hw[4], gw[4], uw[4];
+                    for (int v = 0; v < 2; ++v) {            // 16 columns = 32 bytes per 256-bit access
+                        uint32_t hw[8], gw[8], uw[8];
 #pragma unroll
-                        for (int i = 0; i < 4; ++i) {
-                            hw[i] = pack_bf16(__uint_as_float(acc[v * 8 + 2 * i]), __uint_as_float(acc[v * 8 + 2 * i + 1]));
+                        for (int i = 0; i < 8; ++i) {
+                            hw[i] = pack_bf16(__uint_as_float(acc[v * 16 + 2 * i]), __uint_as_float(acc[v * 16 + 2 * i + 1]));
                             const float2 dhf = unpack_bf16(hw[i]);
-                            float2 gf = unpack_bf16(gin[i]), uf = unpack_bf16(uin[i]);
+                            float2 gf = unpack_bf16(gv[v][i]), uf = unpack_bf16(uv[v][i]);
                             bool gm0 = true, gm1 = true, um0 = true, um1 = true;
                             if (p.has_limit) {
                                 gm0 = gf.x <= p.limit; gm1 = gf.y <= p.limit;
@@ -399,9 +400,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                             uw[i] = pack_bf16(um0 ? silu0 * dhf.x : 0.0f, um1 ? silu1 * dhf.y : 0.0f);
                             partial += dhf.x * inv_w * (silu0 * uf.x) + dhf.y * inv_w * (silu1 * uf.y);
                         }
-                        dh[v] = make_uint4(hw[0], hw[1], hw[2], hw[3]);
-                        dg[v] = make_uint4(gw[0], gw[1], gw[2], gw[3]);
-                        du[v] = make_uint4(uw[0], uw[1], uw[2], uw[3]);
+                        st_global_256(dh + v * 16, hw[0], hw[1], hw[2], hw[3], hw[4], hw[5], hw[6], hw[7]);
+                        st_global_256(dg + v * 16, gw[0], gw[1], gw[2], gw[3], gw[4], gw[5], gw[6], gw[7]);
+                        st_global_256(du + v * 16, uw[0], uw[1], uw[2], uw[3], uw[4], uw[5], uw[6], uw[7]);
                     }
                 }
                 if (p.partials) p.partials[(row * p.n_tiles + n_idx) * kEpiSplit + half] = partial;
