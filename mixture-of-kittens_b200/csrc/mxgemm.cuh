@@ -104,9 +104,7 @@ __device__ __forceinline__ uint64_t make_sf_desc(uint32_t smem_addr) {
 __device__ __forceinline__ void mx_store_normal(const uint32_t (&w)[16], uint8_t* q, uint8_t* sc, size_t row, int col0, int cols) {
     uint32_t out[8], sb;
     mx_quantize_block(w, out, sb);
-    uint4* dst = reinterpret_cast<uint4*>(q + row * cols + col0);
-    dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
-    dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+    st_global_256(q + row * cols + col0, out[0], out[1], out[2], out[3], out[4], out[5], out[6], out[7]);
     sc[mx_scale_offset(static_cast<int>(row), col0 >> 5, cols >> 7)] = static_cast<uint8_t>(sb);
 }
 // quantise the same chunk along the token axis.  The warp's 32 lanes hold rows row0..row0+31 (one MX
@@ -129,9 +127,8 @@ __device__ __forceinline__ void mx_store_transposed(const uint32_t (&w)[16], uin
     }
     mx_quantize_block(in, out, sb);
     const size_t row0 = row - lane;
-    uint4* dst = reinterpret_cast<uint4*>(qt + static_cast<size_t>(col0 + lane) * t_rows + row0);
-    dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
-    dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+    st_global_256(qt + static_cast<size_t>(col0 + lane) * t_rows + row0, out[0], out[1], out[2], out[3], out[4], out[5], out[6],
+                  out[7]);
     sct[mx_scale_offset(col0 + lane, static_cast<int>(row0 >> 5), t_rows >> 7)] = static_cast<uint8_t>(sb);
 }
 
@@ -379,20 +376,21 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 if (!(kWgrad && p.accumulate && k_tiles == 0)) {
                     __nv_bfloat16* dst = p.out_bf16 + (kWgrad ? static_cast<size_t>(expert) * p.out_expert_stride : 0) +
                                          row * p.ld_out + static_cast<size_t>(n_idx) * kBlockN + sub * 64;
-                    uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        uint32_t o[4] = {pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]};
+                    for (int v = 0; v < 4; ++v) {            // 16 columns = 32 bytes per 256-bit access
+                        uint32_t o[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o[i] = pk[8 * v + i];
                         if (kWgrad && p.accumulate) {
-                            const uint4 old = d4[v];
-                            const uint32_t q[4] = {old.x, old.y, old.z, old.w};
+                            uint32_t q[8];
+                            ld_global_256(dst + v * 16, q);
 #pragma unroll
-                            for (int i = 0; i < 4; ++i) {
+                            for (int i = 0; i < 8; ++i) {
                                 const float2 a = unpack_bf16(o[i]), b = unpack_bf16(q[i]);
                                 o[i] = pack_bf16(a.x + b.x, a.y + b.y);
                             }
                         }
-                        d4[v] = make_uint4(o[0], o[1], o[2], o[3]);
+                        st_global_256(dst + v * 16, o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]);
                     }
                 }
             } else if constexpr (kEpi == kMxEpiGateUp) {
@@ -418,21 +416,22 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 if (p.row_scale) { const float w = p.row_scale[row]; inv_w = w > 0.0f ? 1.0f / w : 0.0f; }
                 float partial = 0.0f;
                 const int colbase = n_idx * kBlockN + sub * 64;
-                uint4* dh4 = reinterpret_cast<uint4*>(p.out_bf16 + row * p.ld_out + colbase);
+                __nv_bfloat16* dh16 = p.out_bf16 + row * p.ld_out + colbase;
                 const size_t so0 = mx_scale_offset(static_cast<int>(row), colbase >> 5, p.q_cols >> 7);   // 2 consecutive bytes
                 const uint32_t gsc2 = *reinterpret_cast<const uint16_t*>(p.in_sc[0] + so0);
                 const uint32_t usc2 = *reinterpret_cast<const uint16_t*>(p.in_sc[1] + so0);
-                const uint4* gq = reinterpret_cast<const uint4*>(p.in_q[0] + row * p.q_cols + colbase);
-                const uint4* uq = reinterpret_cast<const uint4*>(p.in_q[1] + row * p.q_cols + colbase);
-                uint4 gv[4], uv[4];
+                uint32_t gv[2][8], uv[2][8];                 // 64 saved fp8 gate / up values each: two 256-bit loads
 #pragma unroll
-                for (int v = 0; v < 4; ++v) { gv[v] = gq[v]; uv[v] = uq[v]; }
+                for (int v = 0; v < 2; ++v) {
+                    ld_global_256(p.in_q[0] + row * p.q_cols + colbase + v * 32, gv[v]);
+                    ld_global_256(p.in_q[1] + row * p.q_cols + colbase + v * 32, uv[v]);
+                }
 #pragma unroll
                 for (int c = 0; c < 2; ++c) {
                     const int col0 = colbase + c * 32;
                     const float gs = mx_scale_value((gsc2 >> (8 * c)) & 0xFFu), us = mx_scale_value((usc2 >> (8 * c)) & 0xFFu);
-                    const uint32_t gb[8] = {gv[2 * c].x, gv[2 * c].y, gv[2 * c].z, gv[2 * c].w, gv[2 * c + 1].x, gv[2 * c + 1].y, gv[2 * c + 1].z, gv[2 * c + 1].w};
-                    const uint32_t ub[8] = {uv[2 * c].x, uv[2 * c].y, uv[2 * c].z, uv[2 * c].w, uv[2 * c + 1].x, uv[2 * c + 1].y, uv[2 * c + 1].z, uv[2 * c + 1].w};
+                    const uint32_t (&gb)[8] = gv[c];
+                    const uint32_t (&ub)[8] = uv[c];
                     uint32_t dg[16], du[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
@@ -455,8 +454,10 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                         partial += dhf.x * inv_w * (silu0 * uf.x) + dhf.y * inv_w * (silu1 * uf.y);
                     }
 #pragma unroll
-                    for (int v = 0; v < 4; ++v)
-                        dh4[c * 4 + v] = make_uint4(pk[c * 16 + 4 * v], pk[c * 16 + 4 * v + 1], pk[c * 16 + 4 * v + 2], pk[c * 16 + 4 * v + 3]);
+                    for (int v = 0; v < 2; ++v)
+                        st_global_256(dh16 + c * 32 + v * 16, pk[c * 16 + 8 * v], pk[c * 16 + 8 * v + 1], pk[c * 16 + 8 * v + 2],
+                                      pk[c * 16 + 8 * v + 3], pk[c * 16 + 8 * v + 4], pk[c * 16 + 8 * v + 5], pk[c * 16 + 8 * v + 6],
+                                      pk[c * 16 + 8 * v + 7]);
                     mx_store_normal(dg, p.q[0], p.sc[0], row, col0, p.q_cols);
                     mx_store_normal(du, p.q[1], p.sc[1], row, col0, p.q_cols);
                     mx_store_transposed(dg, tr, p.qt[0], p.sct[0], row, col0, p.t_rows, lane);
