@@ -378,9 +378,8 @@ __global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, Qu
                 for (int j = 0; j < 16; ++j) { const float2 f = unpack_bf16(in[j]); in[j] = pack_bf16(f.x * w, f.y * w); }
             }
             mx_quantize_block(in, out, sb);
-            uint4* dst = reinterpret_cast<uint4*>(o.q + static_cast<size_t>(row0 + r) * p.hidden + col0 + kb * 32);
-            dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
-            dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+            st_global_256(o.q + static_cast<size_t>(row0 + r) * p.hidden + col0 + kb * 32, out[0], out[1], out[2], out[3], out[4],
+                          out[5], out[6], out[7]);
             o.sc[mx_scale_offset(row0 + r, (col0 >> 5) + kb, p.hidden >> 7)] = static_cast<uint8_t>(sb);
         }
         {   // transposed: thread -> column, block = the 32 rows
@@ -393,9 +392,8 @@ __global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, Qu
                 in[j] = pack_bf16(lo, hi);
             }
             mx_quantize_block(in, out, sb);
-            uint4* dst = reinterpret_cast<uint4*>(o.qt + static_cast<size_t>(col0 + c) * o.t_rows + row0);
-            dst[0] = make_uint4(out[0], out[1], out[2], out[3]);
-            dst[1] = make_uint4(out[4], out[5], out[6], out[7]);
+            st_global_256(o.qt + static_cast<size_t>(col0 + c) * o.t_rows + row0, out[0], out[1], out[2], out[3], out[4], out[5],
+                          out[6], out[7]);
             o.sct[mx_scale_offset(col0 + c, row0 >> 5, o.t_rows >> 7)] = static_cast<uint8_t>(sb);
         }
         __syncthreads();                              // tile `buf` may be refilled
