@@ -8,7 +8,9 @@
  *  - Errors only the device can detect (schedule overflow, a wait that ran out) are written
  *    to the caller's status word: int32[4] in device memory = {code, detail, block, 0},
  *    first error wins.  The library never traps and never waits without a limit.
- *  - The library allocates no device memory.  Callers own inputs, outputs and scratch.
+ *  - The library allocates no device memory.  Callers own inputs, outputs and scratch.  (Its image
+ *    carries one fixed 4 MiB __device__ array, resident on every GPU that loads the library: the
+ *    scratch of mok_schedule_static, see there.)
  *  - "Reference" citations give the file:line of the interface in the Mixture-of-Kittens
  *    project that the entry point stands in for.
  */
@@ -44,6 +46,34 @@ const char* mok_error_string(int code);
  * host thread ("" if none): the detail behind a MOK_ERR_CUDA return.  No reference counterpart. */
 const char* mok_last_cuda_error(void);
 
+/* Sizes, in bytes, of everything a caller has to allocate around the layer for one problem shape: the eight
+ * rank-visible buffers of a workspace (each rank allocates the same sizes and exchanges the addresses), the
+ * barrier state, the status word, the four schedule tables together, and the scheduler's scratch.
+ * schedule_capacity = T * topk * max(2, ceil(ep_size * multiplier)) rows.
+ * Reference: mok/functional.py:160-281 (create_workspace: the same buffers and the same capacity formula,
+ * :196,206), csrc/scheduler.cuh:149-183 (the tables scheduler::schedule allocates). */
+typedef struct mok_workspace_bytes {
+    int64_t schedule_capacity;               /* rows */
+    size_t x_buffer, combine_buffer;         /* bf16 [T, H], [T*K, H] */
+    size_t d_y_buffer, d_x_routed_buffer;    /* bf16 [T, H], [T*K, H] */
+    size_t router_weight_buffer, d_router_weight_buffer;   /* f32 [T, K] */
+    size_t all_gather_top_experts_buffer;    /* i32 [ep_size, T, K] */
+    size_t barrier_buffer, barrier_target;   /* u32 [1] each; both start at zero */
+    size_t status_word;                      /* i32 [4], starts at zero */
+    size_t schedule_tables;                  /* peer_rank + peer_token_idx [cap] + num_tokens [1] + tokens_per_expert [El] */
+    size_t schedule_scratch;                 /* = mok_schedule_scratch_bytes(ep_size, El) */
+} mok_workspace_bytes;
+int mok_query_workspace_bytes(int ep_size, int num_local_tokens, int hidden, int topk, int num_local_experts,
+                              double schedule_capacity_multiplier, mok_workspace_bytes* out);
+
+/* Reads the caller's status word back to the host: copies the four int32 {code, detail, block, 0} from
+ * `status_device` into `out_host`, optionally zeroes the word afterwards, and waits for `stream` (so it also
+ * waits for the layer calls enqueued there).  The layer entry points never synchronise; call this at step
+ * boundaries, where a host synchronisation is acceptable.
+ * Reference: none as a function; it stands where the reference would have trapped (csrc/scheduler.cuh:86) or
+ * spun without limit (csrc/utils.cuh:291-293, csrc/mok_megakernel.cuh:298-302). */
+int mok_last_status(int32_t* status_device, int32_t* out_host, int clear, void* stream);
+
 /* All-gather of the int32 top-k expert ids: rank `rank` stores its `numel` ids into slot `rank`
  * of every peer's [ep_size, numel] buffer with plain peer stores over NVLink.
  * Reference: mok/ops.py:6-58 (all_gather_top_experts), csrc/utils.cuh:230-263. */
@@ -51,8 +81,11 @@ int mok_all_gather_top_experts(const int32_t* top_experts, int64_t numel,
                                const uint64_t* peer_buffer_ptrs, int ep_size, int rank, void* stream);
 
 /* Device-side barrier over the expert-parallel ranks: target += ep_size, every rank adds 1 to
- * each peer's counter, then waits (bounded by `timeout_ns`, 0 = default) until its own counter
- * reaches the target.  On expiry the status word gets MOK_STATUS_BARRIER_TIMEOUT.
+ * each peer's counter, then waits until its own counter reaches the target.  The wait is bounded by
+ * `timeout_ns`; 0 selects the default of two minutes (MOK_B200_BARRIER_TIMEOUT_MS in the environment
+ * overrides the default).  On expiry the status word gets MOK_STATUS_BARRIER_TIMEOUT and the stream carries
+ * on, so the data a later kernel reads from a peer may not be there yet: check the status word at every step
+ * boundary (mok_last_status) and discard the step when it is set.
  * Reference: mok/ops.py:61-100 (barrier_all), csrc/utils.cuh:283-313. */
 int mok_barrier_all(uint32_t* local_counter, const uint64_t* peer_counter_ptrs, int ep_size,
                     uint32_t* target, int32_t* status, uint64_t timeout_ns, void* stream);
@@ -149,9 +182,14 @@ typedef struct mok_layer_common {
     int ep_size, ep_rank;
     int num_local_tokens, hidden, intermediate, num_local_experts, topk;
     int schedule_capacity, macrobatch_size, minibatch_size;
-    int num_comm_sms;                       /* accepted and range-checked by the callers for API compatibility; the row
-                                               movers here are small CTAs that share SMs with the GEMMs, so no SM is
-                                               set aside and the value does not change the launches */
+    int num_comm_sms;                       /* SMs set aside for row movement while the GEMMs run, as the reference's
+                                               fwd/bwd_num_comm_sms (mok/functional.py:22-29): with ep_size > 1 and a
+                                               window cut into chunks (at least two minibatches), dispatch and combine
+                                               run as this many bulk-copy CTAs on SMs of their own and the routed GEMM
+                                               grids shrink by the same number (capped at half the GPU).  With one rank
+                                               the movers are thin CTAs beside the GEMMs and the value is not used.
+                                               MOK_B200_COMM_SMS in the environment overrides it (0 = thin CTAs that
+                                               share SMs with the GEMMs at any ep_size). */
     int has_swiglu_limit;
     float swiglu_limit;
     int defer_combine;                      /* 1: leave the routed results in their rows (y_routed, or d_x_routed and the

@@ -3,6 +3,8 @@
 // two HBM-bound epilogues.  All peer traffic is plain unicast ld/st on peer-mapped addresses;
 // there is no cluster multicast and no library collective on this path.
 #include "comm.cuh"
+
+#include <cstdlib>
 #include "mxfp8.cuh"
 #include "profile.cuh"
 
@@ -453,12 +455,24 @@ extern "C" int mok_all_gather_top_experts(const int32_t* top_experts, int64_t nu
         peers.p[i] = reinterpret_cast<void*>(peer_buffer_ptrs[i]);
     }
     const int64_t n_vec = numel / 4;
-    const int blocks = static_cast<int>(std::min<int64_t>((n_vec + 255) / 256, 296));
+    const int blocks = static_cast<int>(std::min<int64_t>((n_vec + 255) / 256, 2 * device_sm_count()));
     ProfScope prof(kSlotAllGather, static_cast<cudaStream_t>(stream));
     all_gather_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(reinterpret_cast<const int4*>(top_experts), n_vec,
                                                                              numel, peers, ep_size, rank);
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
+}
+
+// Ranks reach a barrier with whatever skew their hosts have (a checkpoint being written, a data loader that
+// stalls), so the default limit is minutes, not the seconds of the in-kernel pipeline waits.
+// MOK_B200_BARRIER_TIMEOUT_MS overrides it.
+static uint64_t default_barrier_timeout_ns() {
+    static const uint64_t configured = [] {
+        const char* e = std::getenv("MOK_B200_BARRIER_TIMEOUT_MS");
+        const long long ms = e ? std::atoll(e) : 0;
+        return static_cast<uint64_t>(ms > 0 ? ms : 120000) * 1000000ull;
+    }();
+    return configured;
 }
 
 extern "C" int mok_barrier_all(uint32_t* local_counter, const uint64_t* peer_counter_ptrs, int ep_size, uint32_t* target,
@@ -472,13 +486,13 @@ extern "C" int mok_barrier_all(uint32_t* local_counter, const uint64_t* peer_cou
     }
     ProfScope prof(kSlotBarrier, static_cast<cudaStream_t>(stream));
     barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(local_counter, peers, ep_size, target, status,
-                                                                    timeout_ns ? timeout_ns : kWaitLimitNs);
+                                                                    timeout_ns ? timeout_ns : default_barrier_timeout_ns());
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
 }
 
 static int epilogue_grid(int64_t total_vec) {
-    return static_cast<int>(std::min<int64_t>((total_vec + 255) / 256, 148 * 16));
+    return static_cast<int>(std::min<int64_t>((total_vec + 255) / 256, 16 * device_sm_count()));
 }
 
 extern "C" int mok_fwd_epilogue(const void* y_shared, const void* combine_buffer, const float* topk_weights, void* output,

@@ -301,6 +301,9 @@ __device__ __forceinline__ void chunk_range(int win_rows, const ChunkSpec& c, in
     hi = (c.index == c.num_chunks - 1) ? win_rows : min(win_rows, lo + per);
 }
 
+// multiprocessor count of the current device (cached per device)
+int device_sm_count();
+
 #define MOK_TRY(expr) do { int rc__ = (expr); if (rc__ != MOK_OK) return rc__; } while (0)
 // where the last failed CUDA call of this host thread was made (read through mok_last_cuda_error)
 void note_cuda_error(cudaError_t err, const char* file, int line);

@@ -425,7 +425,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
 // elem_bytes 1 or 2: 128-byte-swizzled operand tiles; elem_bytes 4: unswizzled rows of 32-bit words (scale tiles)
 int make_tmap_2d(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_bytes,
                  uint32_t box_inner, uint32_t box_outer, int elem_bytes);
-int device_sm_count();
 bool use_pairs();
 
 struct GemmOperands {

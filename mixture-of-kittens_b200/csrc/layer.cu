@@ -9,6 +9,8 @@
 // Backward, per window (first window first; later windows replay dispatch + gate/up):
 //   reverse-combine (w * d_y)  ->  [dgrad down + SwiGLU backward + router-grad partials]
 //   ->  dgrad gate+up (one accumulator)  ->  reverse-dispatch (+ router grads)  ->  3 wgrads
+#include <climits>
+#include <cmath>
 #include <cstdlib>
 #include <mutex>
 #include <vector>
@@ -47,14 +49,17 @@ int fill_peers(PeerPtrs& out, const uint64_t* ptrs, int W) {
     return MOK_OK;
 }
 
-// row sub-range the helpers below put into every routed launch they build (set by the pipeline)
-thread_local ChunkSpec t_chunk = {0, 1, 0};
-thread_local int t_gemm_ctas = 0;     // cap on the CTAs of routed GEMM launches inside the pipeline (0 = all SMs)
-thread_local int t_fat_movers = 0;    // movers run as a few fat CTAs on SMs of their own
+// How the routed launches of one pipeline step are shaped; the pipeline hands one of these to every launch
+// helper, so nothing about a call lives outside its own stack frame.
+struct PassCtx {
+    ChunkSpec chunk = {0, 1, 0};   // row sub-range of the window the launch covers
+    int gemm_ctas = 0;             // cap on the CTAs of routed GEMM launches (0 = all SMs)
+    int comm_sms = 0;              // > 0: the row movers run as this many fat CTAs on SMs of their own
+};
 
-GemmParams base_params(const mok_layer_common& c, bool routed, int off, int limit) {
+GemmParams base_params(const mok_layer_common& c, const PassCtx& x, bool routed, int off, int limit) {
     GemmParams p{};
-    if (routed) p.chunk = t_chunk;
+    if (routed) p.chunk = x.chunk;
     if (routed) {
         p.num_tokens = c.num_tokens;
         p.capacity = c.schedule_capacity;
@@ -76,9 +81,9 @@ GemmParams base_params(const mok_layer_common& c, bool routed, int off, int limi
 
 
 // gate|up GEMM with fused SwiGLU: A [rows, H] K-major, B = (Wg, Wu) [E*I, H] K-major
-int run_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int off, int limit, const void* a, int a_rows,
+int run_gate_up(const mok_layer_common& c, const PassCtx& x, const Dims& d, bool routed, int off, int limit, const void* a, int a_rows,
                 const void* wg, const void* wu, void* gate, void* up, void* hidden, cudaStream_t s) {
-    GemmParams p = base_params(c, routed, off, limit);
+    GemmParams p = base_params(c, x, routed, off, limit);
     p.n_tiles = d.I / (kBlockN / 2);
     p.k_blocks_per_seg = d.H / kBlockK;
     p.b_rows_per_expert = d.I;
@@ -90,14 +95,14 @@ int run_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int off, 
     o.a0 = a; o.b0 = wg; o.b1 = wu;
     o.a_inner = d.H; o.a_outer = a_rows;
     o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.I;
-    return launch_grouped_gemm(kMajorK, kMajorK, kEpiSwigluFwd, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? t_gemm_ctas : 0,
+    return launch_grouped_gemm(kMajorK, kMajorK, kEpiSwigluFwd, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? x.gemm_ctas : 0,
                                routed ? kSlotGateUpRouted : kSlotGateUpShared, s);
 }
 
 // down GEMM: A = hidden [rows, I] K-major, B = Wd [E*H, I] K-major
-int run_down(const mok_layer_common& c, const Dims& d, bool routed, int off, int limit, const void* hidden, int a_rows,
+int run_down(const mok_layer_common& c, const PassCtx& x, const Dims& d, bool routed, int off, int limit, const void* hidden, int a_rows,
              const void* wd, void* y, cudaStream_t s) {
-    GemmParams p = base_params(c, routed, off, limit);
+    GemmParams p = base_params(c, x, routed, off, limit);
     p.n_tiles = d.H / kBlockN;
     p.k_blocks_per_seg = d.I / kBlockK;
     p.b_rows_per_expert = d.H;
@@ -107,15 +112,15 @@ int run_down(const mok_layer_common& c, const Dims& d, bool routed, int off, int
     o.a0 = hidden; o.b0 = wd;
     o.a_inner = d.I; o.a_outer = a_rows;
     o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.H;
-    return launch_grouped_gemm(kMajorK, kMajorK, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? t_gemm_ctas : 0,
+    return launch_grouped_gemm(kMajorK, kMajorK, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? x.gemm_ctas : 0,
                                routed ? kSlotDownRouted : kSlotDownShared, s);
 }
 
 // d_hidden = d_y @ Wd (B is [E*H, I] read N-major), fused SwiGLU backward
-int run_dgrad_down(const mok_layer_common& c, const Dims& d, bool routed, int off, int limit, const void* d_y, int a_rows,
+int run_dgrad_down(const mok_layer_common& c, const PassCtx& x, const Dims& d, bool routed, int off, int limit, const void* d_y, int a_rows,
                    const void* wd, const void* gate, const void* up, void* d_hidden, void* d_gate, void* d_up,
                    const float* row_scale, float* partials, cudaStream_t s) {
-    GemmParams p = base_params(c, routed, off, limit);
+    GemmParams p = base_params(c, x, routed, off, limit);
     p.n_tiles = d.I / kBlockN;
     p.k_blocks_per_seg = d.H / kBlockK;
     p.b_rows_per_expert = d.H;
@@ -131,14 +136,14 @@ int run_dgrad_down(const mok_layer_common& c, const Dims& d, bool routed, int of
     o.a0 = d_y; o.b0 = wd;
     o.a_inner = d.H; o.a_outer = a_rows;
     o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.H;
-    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiSwigluBwd, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? t_gemm_ctas : 0,
+    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiSwigluBwd, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? x.gemm_ctas : 0,
                                routed ? kSlotDgradDownRouted : kSlotDgradDownShared, s);
 }
 
 // d_x = d_gate @ Wg + d_up @ Wu in one accumulator (B = [E*I, H] read N-major)
-int run_dgrad_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int off, int limit, const void* d_gate,
+int run_dgrad_gate_up(const mok_layer_common& c, const PassCtx& x, const Dims& d, bool routed, int off, int limit, const void* d_gate,
                       const void* d_up, int a_rows, const void* wg, const void* wu, void* d_x, cudaStream_t s) {
-    GemmParams p = base_params(c, routed, off, limit);
+    GemmParams p = base_params(c, x, routed, off, limit);
     p.n_tiles = d.H / kBlockN;
     p.k_blocks_per_seg = d.I / kBlockK;
     p.num_segs = 2;
@@ -149,15 +154,15 @@ int run_dgrad_gate_up(const mok_layer_common& c, const Dims& d, bool routed, int
     o.a0 = d_gate; o.a1 = d_up; o.b0 = wg; o.b1 = wu;
     o.a_inner = d.I; o.a_outer = a_rows;
     o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(routed ? d.El : 1) * d.I;
-    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? t_gemm_ctas : 0,
+    return launch_grouped_gemm(kMajorK, kMajorMN, kEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, routed ? x.gemm_ctas : 0,
                                routed ? kSlotDgradGateUpRouted : kSlotDgradGateUpShared, s);
 }
 
 // dW[e] [m, n] = A[rows_e, m]^T @ B[rows_e, n]; both operands are read MN-major straight from the
 // row-major activations
-int run_wgrad(const mok_layer_common& c, bool routed, int off, int limit, const void* a, int m, const void* b, int n,
+int run_wgrad(const mok_layer_common& c, const PassCtx& x, bool routed, int off, int limit, const void* a, int m, const void* b, int n,
               int rows, void* dw, int accumulate, cudaStream_t s) {
-    GemmParams p = base_params(c, routed, off, limit);
+    GemmParams p = base_params(c, x, routed, off, limit);
     p.m_tiles_w = m / kBlockM;
     p.n_tiles = n / kBlockN;
     p.out0 = static_cast<__nv_bfloat16*>(dw);
@@ -173,7 +178,7 @@ int run_wgrad(const mok_layer_common& c, bool routed, int off, int limit, const 
                                routed ? kSlotWgradRouted : kSlotWgradShared, s);
 }
 
-RowMoveParams row_move(const mok_layer_common& c, const Dims& d, int off, int limit, void* local) {
+RowMoveParams row_move(const mok_layer_common& c, const PassCtx& x, const Dims& d, int off, int limit, void* local) {
     RowMoveParams r{};
     r.local = local;
     r.peer_rank = c.schedule_peer_rank;
@@ -185,8 +190,8 @@ RowMoveParams row_move(const mok_layer_common& c, const Dims& d, int off, int li
     r.hidden = d.H;
     r.row_divisor = 1;
     r.status = c.status;
-    r.fat_ctas = t_fat_movers;
-    r.chunk = t_chunk;
+    r.fat_ctas = x.comm_sms > 0 ? 1 : 0;
+    r.chunk = x.chunk;
     return r;
 }
 
@@ -201,95 +206,128 @@ RowMoveParams row_move(const mok_layer_common& c, const Dims& d, int off, int li
 //     main:          compute(0)              compute(1)              ...
 // Dependencies are CUDA events only (no kernel waits on another kernel), the side stream forks from
 // and joins back into the caller's stream inside the call, and results do not depend on timing.
-// The movement kernels are small-footprint CTAs that share SMs with the persistent GEMM CTAs.
+// Two shapes of mover launch: by default thin CTAs that share SMs with the persistent GEMM CTAs; with
+// `comm_sms` > 0 (the reference's fwd/bwd_num_comm_sms) that many fat CTAs on SMs of their own, the
+// routed GEMM grids shrinking by the same number.
+// Even an unchunked window puts its load on the side stream, so that it runs beside whatever the caller's
+// stream holds since the last fork (the dense shared expert: tensor-bound, while the row gather is
+// memory-bound).
 // -------------------------------------------------------------------------------------------------
 namespace mok {
 namespace {
 
-struct DeviceStreams {
-    cudaStream_t side = nullptr;
+// Side streams and events are pooled per device and lent to one call at a time, so two host threads
+// driving the same device never record or wait on each other's events.
+struct DevicePool {
+    std::vector<cudaStream_t> streams;
     std::vector<cudaEvent_t> events;
 };
-DeviceStreams g_streams[64];
-std::mutex g_streams_mu;
+DevicePool g_pool[64];
+std::mutex g_pool_mu;
 
-// SMs set aside for the movers while a window is processed in chunks (0 = movers share SMs with the GEMMs)
-int comm_sm_count() {
-    static const int configured = [] {
-        const char* e = std::getenv("MOK_B200_COMM_SMS");
-        const int v = e ? std::atoi(e) : 0;
-        return v < 0 ? 0 : (v > 64 ? 64 : v);
-    }();
+int env_int(const char* name, int fallback) {
+    const char* e = std::getenv(name);
+    return e ? std::atoi(e) : fallback;
+}
+
+// MOK_B200_COMM_SMS: -1 / unset = take the count from the call's num_comm_sms; 0 = thin movers that share
+// SMs with the GEMMs whatever the call says; n > 0 = n SMs whatever the call says
+int comm_sm_override() {
+    static const int configured = [] { const int v = env_int("MOK_B200_COMM_SMS", -1); return v > 64 ? 64 : v; }();
     return configured;
+}
+bool overlap_shared_expert() {
+    static const bool on = env_int("MOK_B200_OVERLAP_SHARED", 1) != 0;
+    return on;
 }
 
 class Pipeline {
 public:
-    Pipeline(cudaStream_t main, int chunks, int min_rows) : main_(main), chunks_(chunks), min_rows_(min_rows) {
-        int dev = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { note_error_text("cudaGetDevice failed or device index >= 64"); rc_ = MOK_ERR_CUDA; return; }
-        ds_ = &g_streams[dev];
-        std::lock_guard<std::mutex> lock(g_streams_mu);
-        if (chunks_ > 1 && ds_->side == nullptr) {
-            int lo = 0, hi = 0;
-            cudaDeviceGetStreamPriorityRange(&lo, &hi);
-            if (cudaStreamCreateWithPriority(&ds_->side, cudaStreamNonBlocking, hi) != cudaSuccess) rc_ = MOK_ERR_CUDA;
+    Pipeline(cudaStream_t main, int chunks, int min_rows, int comm_sms)
+        : main_(main), chunks_(chunks), min_rows_(min_rows), comm_sms_(comm_sms) {
+        if (cudaGetDevice(&dev_) != cudaSuccess || dev_ < 0 || dev_ >= 64) {
+            note_error_text("cudaGetDevice failed or device index >= 64");
+            rc_ = MOK_ERR_CUDA;
+            return;
         }
+        use_side_ = chunks_ > 1 || overlap_shared_expert();
+        if (!use_side_) return;
+        std::lock_guard<std::mutex> lock(g_pool_mu);
+        DevicePool& pool = g_pool[dev_];
+        if (!pool.streams.empty()) { side_ = pool.streams.back(); pool.streams.pop_back(); return; }
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        if (cudaStreamCreateWithPriority(&side_, cudaStreamNonBlocking, hi) != cudaSuccess) { side_ = nullptr; rc_ = MOK_ERR_CUDA; }
     }
+    // Every exit path of a layer call ends here: the side stream is joined back into the caller's stream
+    // (an open stream capture stays well-formed after an error) and the borrowed objects return to the pool.
+    ~Pipeline() {
+        if (side_ && forked_) order(side_, main_);
+        std::lock_guard<std::mutex> lock(g_pool_mu);
+        DevicePool& pool = g_pool[dev_ >= 0 && dev_ < 64 ? dev_ : 0];
+        if (side_) pool.streams.push_back(side_);
+        for (cudaEvent_t e : held_) pool.events.push_back(e);
+    }
+    Pipeline(const Pipeline&) = delete;
+    Pipeline& operator=(const Pipeline&) = delete;
     int error() const { return rc_; }
 
     // side stream continues after everything enqueued on main so far / main after side
-    int fork() { return chunks_ > 1 ? order(main_, ds_->side) : MOK_OK; }
-    int join() { return chunks_ > 1 ? order(ds_->side, main_) : MOK_OK; }
+    int fork() { if (!use_side_) return MOK_OK; forked_ = true; return order(main_, side_); }
+    int join() { if (!use_side_ || !forked_) return MOK_OK; forked_ = false; return order(side_, main_); }
 
-    // load(c) and store(c) are enqueued on side(), compute(c) on main(); t_chunk selects chunk c
+    // load(stream, ctx) and store(stream, ctx) go to the side stream, compute(stream, ctx) to the caller's.
     // Only window 0 is cut into chunks: later windows hold rows only when the schedule exceeds one
     // macrobatch, and an empty launch is cheaper than eight of them.
     template <class Load, class Compute, class Store>
     int run(bool chunked, Load load, Compute compute, Store store) {
         if (rc_ != MOK_OK) return rc_;
-        if (chunks_ <= 1 || !chunked) {
-            t_chunk = ChunkSpec{0, 1, 0};
-            int rc;
-            if ((rc = load(main_))) return rc;
-            if ((rc = compute(main_))) return rc;
-            return store(main_);
-        }
         int rc = MOK_OK;
-        const int comm_sms = comm_sm_count();
-        if (comm_sms > 0) { t_gemm_ctas = device_sm_count() - comm_sms; t_fat_movers = 1; }
-        std::vector<cudaEvent_t> loaded(chunks_);
-        set_chunk(0);
-        if ((rc = load(ds_->side))) return finish(rc);
-        if ((rc = record(ds_->side, loaded[0]))) return finish(rc);
-        for (int c = 0; c < chunks_ && rc == MOK_OK; ++c) {
-            if (c + 1 < chunks_) {
-                set_chunk(c + 1);
-                if ((rc = load(ds_->side))) break;
-                if ((rc = record(ds_->side, loaded[c + 1]))) break;
+        if (chunks_ <= 1 || !chunked) {
+            PassCtx x;
+            if (use_side_ && forked_) {
+                if ((rc = load(side_, x))) return rc;
+                if ((rc = join())) return rc;
+            } else if ((rc = load(main_, x))) {
+                return rc;
             }
-            set_chunk(c);
-            if (cudaStreamWaitEvent(main_, loaded[c], 0) != cudaSuccess) { rc = MOK_ERR_CUDA; break; }
-            if ((rc = compute(main_))) break;
-            cudaEvent_t computed;
-            if ((rc = record(main_, computed))) break;
-            if (cudaStreamWaitEvent(ds_->side, computed, 0) != cudaSuccess) { rc = MOK_ERR_CUDA; break; }
-            if ((rc = store(ds_->side))) break;
+            if ((rc = compute(main_, x))) return rc;
+            return store(main_, x);
         }
-        return finish(rc);
+        if (!forked_ && (rc = fork())) return rc;
+        std::vector<cudaEvent_t> loaded(chunks_);
+        if ((rc = load(side_, ctx(0)))) return rc;
+        if ((rc = record(side_, loaded[0]))) return rc;
+        for (int c = 0; c < chunks_; ++c) {
+            if (c + 1 < chunks_) {
+                if ((rc = load(side_, ctx(c + 1)))) return rc;
+                if ((rc = record(side_, loaded[c + 1]))) return rc;
+            }
+            if (cudaStreamWaitEvent(main_, loaded[c], 0) != cudaSuccess) return MOK_ERR_CUDA;
+            if ((rc = compute(main_, ctx(c)))) return rc;
+            cudaEvent_t computed;
+            if ((rc = record(main_, computed))) return rc;
+            if (cudaStreamWaitEvent(side_, computed, 0) != cudaSuccess) return MOK_ERR_CUDA;
+            if ((rc = store(side_, ctx(c)))) return rc;
+        }
+        return MOK_OK;
     }
 
 private:
-    void set_chunk(int c) { t_chunk = ChunkSpec{c, chunks_, min_rows_}; }
-    int finish(int rc) { t_chunk = ChunkSpec{0, 1, 0}; t_gemm_ctas = 0; t_fat_movers = 0; return rc; }
+    PassCtx ctx(int c) const {
+        PassCtx x;
+        x.chunk = ChunkSpec{c, chunks_, min_rows_};
+        if (comm_sms_ > 0) { x.comm_sms = comm_sms_; x.gemm_ctas = device_sm_count() - comm_sms_; }
+        return x;
+    }
     int record(cudaStream_t s, cudaEvent_t& out) {
-        std::lock_guard<std::mutex> lock(g_streams_mu);
-        if (next_ == ds_->events.size()) {
-            cudaEvent_t e = nullptr;
-            if (cudaEventCreateWithFlags(&e, cudaEventDisableTiming) != cudaSuccess) return MOK_ERR_CUDA;
-            ds_->events.push_back(e);
+        {
+            std::lock_guard<std::mutex> lock(g_pool_mu);
+            DevicePool& pool = g_pool[dev_];
+            if (!pool.events.empty()) { out = pool.events.back(); pool.events.pop_back(); }
+            else if (cudaEventCreateWithFlags(&out, cudaEventDisableTiming) != cudaSuccess) return MOK_ERR_CUDA;
         }
-        out = ds_->events[next_++];
+        held_.push_back(out);
         return cudaEventRecord(out, s) == cudaSuccess ? MOK_OK : MOK_ERR_CUDA;
     }
     int order(cudaStream_t first, cudaStream_t then) {
@@ -299,35 +337,40 @@ private:
         return cudaStreamWaitEvent(then, e, 0) == cudaSuccess ? MOK_OK : MOK_ERR_CUDA;
     }
     cudaStream_t main_;
-    int chunks_, min_rows_;
-    DeviceStreams* ds_ = nullptr;
-    size_t next_ = 0;
+    cudaStream_t side_ = nullptr;
+    int chunks_, min_rows_, comm_sms_;
+    int dev_ = -1;
+    bool use_side_ = false, forked_ = false;
+    std::vector<cudaEvent_t> held_;
     int rc_ = MOK_OK;
 };
 
-// CTAs of a row-movement launch.  Inside the pipeline they share the SMs with the persistent GEMM CTAs.
-int move_grid_thin();
-int move_grid() { return t_fat_movers ? comm_sm_count() : move_grid_thin(); }
-int move_grid_thin() {
-    static const int configured = [] {
-        const char* e = std::getenv("MOK_B200_COMM_BLOCKS");
-        return e ? std::atoi(e) : 0;
-    }();
+// CTAs of a row-movement launch: the dedicated SMs' worth of fat CTAs, or thin CTAs that share the SMs with
+// the persistent GEMM CTAs (four per SM; MOK_B200_COMM_BLOCKS overrides)
+int move_grid(const PassCtx& x) {
+    if (x.comm_sms > 0) return x.comm_sms;
+    static const int configured = env_int("MOK_B200_COMM_BLOCKS", 0);
     return configured > 0 ? configured : device_sm_count() * 4;
 }
 
 int pipeline_chunks(const mok_layer_common& c, int limit) {
-    static const int configured = [] {
-        const char* e = std::getenv("MOK_B200_CHUNKS");
-        const int v = e ? std::atoi(e) : 0;
-        return v < 0 ? 0 : (v > 32 ? 32 : v);
-    }();
+    static const int configured = [] { const int v = env_int("MOK_B200_CHUNKS", 0); return v < 0 ? 0 : (v > 32 ? 32 : v); }();
     // default: no chunking on a single rank (movement and GEMMs compete for HBM there), four chunks
     // when rows cross NVLink (measured at 2 and 8 ranks: 2, 4, 8 and 16 chunks are within 4 % of each
     // other, 4 the shortest)
     const int want = configured > 0 ? configured : (c.ep_size > 1 ? 4 : 1);
     const int by_minibatch = limit / c.minibatch_size;
     return std::max(1, std::min(want, by_minibatch));
+}
+
+// SMs set aside for the row movers of this call: the caller's num_comm_sms when rows cross NVLink and the
+// window is processed in chunks, unless the environment overrides it; never more than half of the GPU
+int pipeline_comm_sms(const mok_layer_common& c, int chunks) {
+    if (chunks <= 1) return 0;
+    const int forced = comm_sm_override();
+    int n = forced >= 0 ? forced : (c.ep_size > 1 ? c.num_comm_sms : 0);
+    n = std::max(0, std::min(n, device_sm_count() / 2));
+    return n & ~1;
 }
 
 }  // namespace
@@ -345,36 +388,38 @@ extern "C" int mok_fwd_bf16(const mok_fwd_bf16_args* a, void* stream) {
     MOK_TRY(fill_peers(x_peers, a->x_ptrs, d.W));
     MOK_TRY(fill_peers(combine_peers, a->combine_buffer_ptrs, d.W));
     const void* x_local = x_peers.p[d.rank];
-    Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
+    const int chunks = pipeline_chunks(c, std::min(d.MB, d.cap));
+    Pipeline pipe(s, chunks, c.minibatch_size, pipeline_comm_sms(c, chunks));
+    const PassCtx whole;       // launches outside the chunked pipeline cover their whole window on all SMs
     MOK_TRY(pipe.error());
     MOK_TRY(pipe.fork());
 
     // shared expert on the local tokens (overlaps the first dispatch chunk)
-    MOK_TRY(run_gate_up(c, d, false, 0, d.T, x_local, d.T, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
+    MOK_TRY(run_gate_up(c, whole, d, false, 0, d.T, x_local, d.T, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
                         a->hidden_shared, s));
-    MOK_TRY(run_down(c, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
+    MOK_TRY(run_down(c, whole, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
 
     const int n_macro = (d.cap + d.MB - 1) / d.MB;
     for (int m = n_macro - 1; m >= 0; --m) {
         const int off = m * d.MB;
         const int limit = std::min(d.MB, d.cap - off);
         MOK_TRY(pipe.run(m == 0,
-            [&](cudaStream_t st) {
-                RowMoveParams disp = row_move(c, d, off, limit, a->x_routed);
+            [&](cudaStream_t st, const PassCtx& x) {
+                RowMoveParams disp = row_move(c, x, d, off, limit, a->x_routed);
                 disp.peers = x_peers;
                 disp.row_divisor = d.K;
-                return launch_dispatch_rows(disp, false, move_grid(), st);
+                return launch_dispatch_rows(disp, false, move_grid(x), st);
             },
-            [&](cudaStream_t st) {
-                MOK_TRY(run_gate_up(c, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up,
+            [&](cudaStream_t st, const PassCtx& x) {
+                MOK_TRY(run_gate_up(c, x, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up,
                                     a->gate_routed, a->up_routed, a->hidden_routed, st));
-                return run_down(c, d, true, off, limit, a->hidden_routed, d.MB, a->w_routed_down, a->y_routed, st);
+                return run_down(c, x, d, true, off, limit, a->hidden_routed, d.MB, a->w_routed_down, a->y_routed, st);
             },
-            [&](cudaStream_t st) {
+            [&](cudaStream_t st, const PassCtx& x) {
                 if (c.defer_combine) return static_cast<int>(MOK_OK);   // mok_fwd_epilogue_rows reads y_routed in place
-                RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
+                RowMoveParams comb = row_move(c, x, d, off, limit, a->y_routed);
                 comb.peers = combine_peers;
-                return launch_combine_rows(comb, move_grid(), st);
+                return launch_combine_rows(comb, move_grid(x), st);
             }));
         MOK_TRY(pipe.join());      // the next window reuses the buffers
         if (m > 0) MOK_TRY(pipe.fork());
@@ -398,67 +443,107 @@ extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
     const void* dy_local = dy_peers.p[d.rank];
     const void* x_local = x_peers.p[d.rank];
     const int partial_cols = d.I / kBlockN * kEpiSplit;
-    Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
+    const int chunks = pipeline_chunks(c, std::min(d.MB, d.cap));
+    Pipeline pipe(s, chunks, c.minibatch_size, pipeline_comm_sms(c, chunks));
+    const PassCtx whole;       // launches outside the chunked pipeline cover their whole window on all SMs
     MOK_TRY(pipe.error());
     MOK_TRY(pipe.fork());
 
     // shared expert (overlaps the first reverse-combine chunk)
-    MOK_TRY(run_dgrad_down(c, d, false, 0, d.T, dy_local, d.T, a->w_shared_down, a->gate_shared, a->up_shared,
+    MOK_TRY(run_dgrad_down(c, whole, d, false, 0, d.T, dy_local, d.T, a->w_shared_down, a->gate_shared, a->up_shared,
                            a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, nullptr, s));
-    MOK_TRY(run_dgrad_gate_up(c, d, false, 0, d.T, a->d_gate_shared, a->d_up_shared, d.T, a->w_shared_gate, a->w_shared_up,
+    MOK_TRY(run_dgrad_gate_up(c, whole, d, false, 0, d.T, a->d_gate_shared, a->d_up_shared, d.T, a->w_shared_gate, a->w_shared_up,
                               a->d_x_shared, s));
-    MOK_TRY(run_wgrad(c, false, 0, d.T, dy_local, d.H, a->hidden_shared, d.I, d.T, a->d_w_shared_down, 0, s));
-    MOK_TRY(run_wgrad(c, false, 0, d.T, a->d_gate_shared, d.I, x_local, d.H, d.T, a->d_w_shared_gate, 0, s));
-    MOK_TRY(run_wgrad(c, false, 0, d.T, a->d_up_shared, d.I, x_local, d.H, d.T, a->d_w_shared_up, 0, s));
+    MOK_TRY(run_wgrad(c, whole, false, 0, d.T, dy_local, d.H, a->hidden_shared, d.I, d.T, a->d_w_shared_down, 0, s));
+    MOK_TRY(run_wgrad(c, whole, false, 0, d.T, a->d_gate_shared, d.I, x_local, d.H, d.T, a->d_w_shared_gate, 0, s));
+    MOK_TRY(run_wgrad(c, whole, false, 0, d.T, a->d_up_shared, d.I, x_local, d.H, d.T, a->d_w_shared_up, 0, s));
 
     const int n_macro = (d.cap + d.MB - 1) / d.MB;
     for (int m = 0; m < n_macro; ++m) {
         const int off = m * d.MB;
         const int limit = std::min(d.MB, d.cap - off);
         if (m > 0) {   // replay the forward of this window into the saved-activation buffers
-            RowMoveParams disp = row_move(c, d, off, limit, a->x_routed);
+            RowMoveParams disp = row_move(c, whole, d, off, limit, a->x_routed);
             disp.peers = x_peers;
             disp.row_divisor = d.K;
-            MOK_TRY(launch_dispatch_rows(disp, false, move_grid(), s));
-            MOK_TRY(run_gate_up(c, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up, a->gate_routed,
+            MOK_TRY(launch_dispatch_rows(disp, false, move_grid(whole), s));
+            MOK_TRY(run_gate_up(c, whole, d, true, off, limit, a->x_routed, d.MB, a->w_routed_gate, a->w_routed_up, a->gate_routed,
                                 a->up_routed, a->hidden_routed, s));
             MOK_TRY(pipe.fork());
         }
         MOK_TRY(pipe.run(m == 0,
-            [&](cudaStream_t st) {
-                RowMoveParams rc = row_move(c, d, off, limit, a->d_y_routed);
+            [&](cudaStream_t st, const PassCtx& x) {
+                RowMoveParams rc = row_move(c, x, d, off, limit, a->d_y_routed);
                 rc.peers = dy_peers;
                 rc.scale_peers = rw_peers;
                 rc.row_divisor = d.K;
                 rc.row_scale_out = a->router_weights_routed;
-                return launch_dispatch_rows(rc, true, move_grid(), st);
+                return launch_dispatch_rows(rc, true, move_grid(x), st);
             },
-            [&](cudaStream_t st) {
-                MOK_TRY(run_dgrad_down(c, d, true, off, limit, a->d_y_routed, d.MB, a->w_routed_down, a->gate_routed,
+            [&](cudaStream_t st, const PassCtx& x) {
+                MOK_TRY(run_dgrad_down(c, x, d, true, off, limit, a->d_y_routed, d.MB, a->w_routed_down, a->gate_routed,
                                        a->up_routed, a->d_hidden_routed, a->d_gate_routed, a->d_up_routed,
                                        a->router_weights_routed, a->d_router_weight_partials, st));
-                return run_dgrad_gate_up(c, d, true, off, limit, a->d_gate_routed, a->d_up_routed, d.MB, a->w_routed_gate,
+                return run_dgrad_gate_up(c, x, d, true, off, limit, a->d_gate_routed, a->d_up_routed, d.MB, a->w_routed_gate,
                                          a->w_routed_up, a->d_x_routed, st);
             },
-            [&](cudaStream_t st) {
-                RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
+            [&](cudaStream_t st, const PassCtx& x) {
+                RowMoveParams rd = row_move(c, x, d, off, limit, a->d_x_routed);
                 if (c.defer_combine) return static_cast<int>(MOK_OK);   // mok_bwd_epilogue_rows reads the rows in place
                 rd.peers = dxr_peers;
                 rd.scale_peers = drw_peers;
                 rd.partials = a->d_router_weight_partials;
                 rd.partial_cols = partial_cols;
-                return launch_combine_rows(rd, move_grid(), st);
+                return launch_combine_rows(rd, move_grid(x), st);
             }));
         MOK_TRY(pipe.join());
         const int acc = m > 0 ? 1 : 0;
-        MOK_TRY(run_wgrad(c, true, off, limit, a->d_y_routed, d.H, a->hidden_routed, d.I, d.MB, a->d_w_routed_down, acc, s));
-        MOK_TRY(run_wgrad(c, true, off, limit, a->d_gate_routed, d.I, a->x_routed, d.H, d.MB, a->d_w_routed_gate, acc, s));
-        MOK_TRY(run_wgrad(c, true, off, limit, a->d_up_routed, d.I, a->x_routed, d.H, d.MB, a->d_w_routed_up, acc, s));
+        MOK_TRY(run_wgrad(c, whole, true, off, limit, a->d_y_routed, d.H, a->hidden_routed, d.I, d.MB, a->d_w_routed_down, acc, s));
+        MOK_TRY(run_wgrad(c, whole, true, off, limit, a->d_gate_routed, d.I, a->x_routed, d.H, d.MB, a->d_w_routed_gate, acc, s));
+        MOK_TRY(run_wgrad(c, whole, true, off, limit, a->d_up_routed, d.I, a->x_routed, d.H, d.MB, a->d_w_routed_up, acc, s));
     }
     return MOK_OK;
 }
 
-extern "C" int mok_version(void) { return 100; }
+extern "C" int mok_version(void) { return 101; }
+
+extern "C" int mok_query_workspace_bytes(int ep_size, int num_local_tokens, int hidden, int topk, int num_local_experts,
+                                         double schedule_capacity_multiplier, mok_workspace_bytes* out) {
+    if (!out) return MOK_ERR_INVALID;
+    if (ep_size < 1 || ep_size > MOK_MAX_PEERS || num_local_tokens <= 0 || num_local_tokens % 256 || hidden <= 0 || hidden % 256)
+        return MOK_ERR_INVALID;
+    if (topk < 1 || topk > 255 || num_local_experts < 1 || num_local_experts > MOK_MAX_LOCAL_EXPERTS) return MOK_ERR_INVALID;
+    if (!(schedule_capacity_multiplier > 0.0) || schedule_capacity_multiplier > 1e6) return MOK_ERR_INVALID;
+    const long long routes = static_cast<long long>(num_local_tokens) * topk;
+    long long factor = static_cast<long long>(std::ceil(ep_size * schedule_capacity_multiplier));
+    if (factor < 2) factor = 2;
+    const long long capacity = routes * factor;
+    if (capacity > INT32_MAX) return MOK_ERR_TOO_LARGE;
+    const size_t T = static_cast<size_t>(num_local_tokens), H = static_cast<size_t>(hidden), R = static_cast<size_t>(routes);
+    out->schedule_capacity = capacity;
+    out->x_buffer = T * H * 2;
+    out->combine_buffer = R * H * 2;
+    out->d_y_buffer = T * H * 2;
+    out->d_x_routed_buffer = R * H * 2;
+    out->router_weight_buffer = R * 4;
+    out->d_router_weight_buffer = R * 4;
+    out->all_gather_top_experts_buffer = static_cast<size_t>(ep_size) * R * 4;
+    out->barrier_buffer = 4;
+    out->barrier_target = 4;
+    out->status_word = 16;
+    out->schedule_tables = static_cast<size_t>(capacity) * 4 * 2 + 4 + static_cast<size_t>(num_local_experts) * 4;
+    out->schedule_scratch = mok_schedule_scratch_bytes(ep_size, num_local_experts);
+    return MOK_OK;
+}
+
+extern "C" int mok_last_status(int32_t* status_device, int32_t* out_host, int clear, void* stream) {
+    if (!status_device || !out_host) return MOK_ERR_INVALID;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MOK_CUDA_CHECK(cudaMemcpyAsync(out_host, status_device, 4 * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    if (clear) MOK_CUDA_CHECK(cudaMemsetAsync(status_device, 0, 4 * sizeof(int32_t), s));
+    MOK_CUDA_CHECK(cudaStreamSynchronize(s));
+    return MOK_OK;
+}
 
 extern "C" const char* mok_error_string(int code) {
     switch (code) {
@@ -485,9 +570,9 @@ extern "C" const char* mok_error_string(int code) {
 namespace mok {
 namespace {
 
-MxGemmParams mx_base(const mok_layer_common& c, int off, int limit) {
+MxGemmParams mx_base(const mok_layer_common& c, const PassCtx& x, int off, int limit) {
     MxGemmParams p{};
-    p.chunk = t_chunk;
+    p.chunk = x.chunk;
     p.num_tokens = c.num_tokens;
     p.capacity = c.schedule_capacity;
     p.tokens_per_expert = c.tokens_per_expert;
@@ -505,10 +590,10 @@ MxGemmParams mx_base(const mok_layer_common& c, int off, int limit) {
 inline uint8_t* u8(void* p) { return static_cast<uint8_t*>(p); }
 inline const uint8_t* cu8(const void* p) { return static_cast<const uint8_t*>(p); }
 
-int mx_gate_up(const mok_layer_common& c, const Dims& d, int off, int limit, const void* x_q, const void* x_sc,
+int mx_gate_up(const mok_layer_common& c, const PassCtx& x, const Dims& d, int off, int limit, const void* x_q, const void* x_sc,
                const void* wg_q, const void* wg_sc, const void* wu_q, const void* wu_sc, void* gate_q, void* gate_sc,
                void* up_q, void* up_sc, void* hid_q, void* hid_sc, void* hid_qt, void* hid_sct, cudaStream_t s) {
-    MxGemmParams p = mx_base(c, off, limit);
+    MxGemmParams p = mx_base(c, x, off, limit);
     p.n_tiles = d.I / (kBlockN / 2);
     p.k_tiles_per_seg = d.H / kMxBlockK;
     p.b_rows_per_expert = d.I;
@@ -522,12 +607,12 @@ int mx_gate_up(const mok_layer_common& c, const Dims& d, int off, int limit, con
     o.a0 = x_q; o.b0 = wg_q; o.b1 = wu_q;
     o.a_inner = d.H; o.a_outer = d.MB;
     o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(d.El) * d.I;
-    return launch_mx_gemm(kMxEpiGateUp, false, o, p, (limit / kBlockM) * p.n_tiles, t_gemm_ctas, kSlotGateUpRouted, s);
+    return launch_mx_gemm(kMxEpiGateUp, false, o, p, (limit / kBlockM) * p.n_tiles, x.gemm_ctas, kSlotGateUpRouted, s);
 }
 
-int mx_down(const mok_layer_common& c, const Dims& d, int off, int limit, const void* hid_q, const void* hid_sc,
+int mx_down(const mok_layer_common& c, const PassCtx& x, const Dims& d, int off, int limit, const void* hid_q, const void* hid_sc,
             const void* wd_q, const void* wd_sc, void* y, cudaStream_t s) {
-    MxGemmParams p = mx_base(c, off, limit);
+    MxGemmParams p = mx_base(c, x, off, limit);
     p.n_tiles = d.H / kBlockN;
     p.k_tiles_per_seg = d.I / kMxBlockK;
     p.b_rows_per_expert = d.H;
@@ -539,12 +624,12 @@ int mx_down(const mok_layer_common& c, const Dims& d, int off, int limit, const 
     o.a0 = hid_q; o.b0 = wd_q;
     o.a_inner = d.I; o.a_outer = d.MB;
     o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(d.El) * d.H;
-    return launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, t_gemm_ctas, kSlotDownRouted, s);
+    return launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, x.gemm_ctas, kSlotDownRouted, s);
 }
 
-int mx_wgrad(const mok_layer_common& c, const Dims& d, int off, int limit, const void* a_qt, const void* a_sct, int m,
+int mx_wgrad(const mok_layer_common& c, const PassCtx& x, const Dims& d, int off, int limit, const void* a_qt, const void* a_sct, int m,
              const void* b_qt, const void* b_sct, int n, void* dw, int accumulate, cudaStream_t s) {
-    MxGemmParams p = mx_base(c, off, limit);
+    MxGemmParams p = mx_base(c, x, off, limit);
     p.m_tiles_w = m / kBlockM;
     p.n_tiles = n / kBlockN;
     p.sfa0 = cu8(a_sct); p.sfa_k_tiles = d.MB / 128;
@@ -573,38 +658,40 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
     MOK_TRY(fill_peers(x_peers, a->x_ptrs, d.W));
     MOK_TRY(fill_peers(combine_peers, a->combine_buffer_ptrs, d.W));
     const void* x_local = x_peers.p[d.rank];
-    Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
+    const int chunks = pipeline_chunks(c, std::min(d.MB, d.cap));
+    Pipeline pipe(s, chunks, c.minibatch_size, pipeline_comm_sms(c, chunks));
+    const PassCtx whole;       // launches outside the chunked pipeline cover their whole window on all SMs
     MOK_TRY(pipe.error());
     MOK_TRY(pipe.fork());
 
-    MOK_TRY(run_gate_up(c, d, false, 0, d.T, x_local, d.T, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
+    MOK_TRY(run_gate_up(c, whole, d, false, 0, d.T, x_local, d.T, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
                         a->hidden_shared, s));
-    MOK_TRY(run_down(c, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
+    MOK_TRY(run_down(c, whole, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
 
     const int n_macro = (d.cap + d.MB - 1) / d.MB;
     for (int m = n_macro - 1; m >= 0; --m) {
         const int off = m * d.MB;
         const int limit = std::min(d.MB, d.cap - off);
         MOK_TRY(pipe.run(m == 0,
-            [&](cudaStream_t st) {
-                RowMoveParams disp = row_move(c, d, off, limit, nullptr);
+            [&](cudaStream_t st, const PassCtx& x) {
+                RowMoveParams disp = row_move(c, x, d, off, limit, nullptr);
                 disp.peers = x_peers;
                 disp.row_divisor = d.K;
                 QuantOut xo{u8(a->work_x_q), u8(a->work_x_sc), u8(a->x_qt), u8(a->x_sct), d.MB};
-                return launch_dispatch_quant(disp, xo, false, move_grid(), st);
+                return launch_dispatch_quant(disp, xo, false, move_grid(x), st);
             },
-            [&](cudaStream_t st) {
-                MOK_TRY(mx_gate_up(c, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
+            [&](cudaStream_t st, const PassCtx& x) {
+                MOK_TRY(mx_gate_up(c, x, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
                                    a->w_routed_up_q, a->w_routed_up_sc, a->gate_q, a->gate_sc, a->up_q, a->up_sc,
                                    a->work_hidden_q, a->work_hidden_sc, a->hidden_qt, a->hidden_sct, st));
-                return mx_down(c, d, off, limit, a->work_hidden_q, a->work_hidden_sc, a->w_routed_down_q,
+                return mx_down(c, x, d, off, limit, a->work_hidden_q, a->work_hidden_sc, a->w_routed_down_q,
                                a->w_routed_down_sc, a->y_routed, st);
             },
-            [&](cudaStream_t st) {
+            [&](cudaStream_t st, const PassCtx& x) {
                 if (c.defer_combine) return static_cast<int>(MOK_OK);   // mok_fwd_epilogue_rows reads y_routed in place
-                RowMoveParams comb = row_move(c, d, off, limit, a->y_routed);
+                RowMoveParams comb = row_move(c, x, d, off, limit, a->y_routed);
                 comb.peers = combine_peers;
-                return launch_combine_rows(comb, move_grid(), st);
+                return launch_combine_rows(comb, move_grid(x), st);
             }));
         MOK_TRY(pipe.join());
         if (m > 0) MOK_TRY(pipe.fork());
@@ -628,47 +715,49 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
     const void* dy_local = dy_peers.p[d.rank];
     const void* x_local = x_peers.p[d.rank];
     const int partial_cols = d.I / kBlockN;
-    Pipeline pipe(s, pipeline_chunks(c, std::min(d.MB, d.cap)), c.minibatch_size);
+    const int chunks = pipeline_chunks(c, std::min(d.MB, d.cap));
+    Pipeline pipe(s, chunks, c.minibatch_size, pipeline_comm_sms(c, chunks));
+    const PassCtx whole;       // launches outside the chunked pipeline cover their whole window on all SMs
     MOK_TRY(pipe.error());
     MOK_TRY(pipe.fork());
 
     // shared expert, BF16
-    MOK_TRY(run_dgrad_down(c, d, false, 0, d.T, dy_local, d.T, a->w_shared_down, a->gate_shared, a->up_shared,
+    MOK_TRY(run_dgrad_down(c, whole, d, false, 0, d.T, dy_local, d.T, a->w_shared_down, a->gate_shared, a->up_shared,
                            a->d_hidden_shared, a->d_gate_shared, a->d_up_shared, nullptr, nullptr, s));
-    MOK_TRY(run_dgrad_gate_up(c, d, false, 0, d.T, a->d_gate_shared, a->d_up_shared, d.T, a->w_shared_gate, a->w_shared_up,
+    MOK_TRY(run_dgrad_gate_up(c, whole, d, false, 0, d.T, a->d_gate_shared, a->d_up_shared, d.T, a->w_shared_gate, a->w_shared_up,
                               a->d_x_shared, s));
-    MOK_TRY(run_wgrad(c, false, 0, d.T, dy_local, d.H, a->hidden_shared, d.I, d.T, a->d_w_shared_down, 0, s));
-    MOK_TRY(run_wgrad(c, false, 0, d.T, a->d_gate_shared, d.I, x_local, d.H, d.T, a->d_w_shared_gate, 0, s));
-    MOK_TRY(run_wgrad(c, false, 0, d.T, a->d_up_shared, d.I, x_local, d.H, d.T, a->d_w_shared_up, 0, s));
+    MOK_TRY(run_wgrad(c, whole, false, 0, d.T, dy_local, d.H, a->hidden_shared, d.I, d.T, a->d_w_shared_down, 0, s));
+    MOK_TRY(run_wgrad(c, whole, false, 0, d.T, a->d_gate_shared, d.I, x_local, d.H, d.T, a->d_w_shared_gate, 0, s));
+    MOK_TRY(run_wgrad(c, whole, false, 0, d.T, a->d_up_shared, d.I, x_local, d.H, d.T, a->d_w_shared_up, 0, s));
 
     const int n_macro = (d.cap + d.MB - 1) / d.MB;
     for (int m = 0; m < n_macro; ++m) {
         const int off = m * d.MB;
         const int limit = std::min(d.MB, d.cap - off);
         if (m > 0) {   // replay dispatch + gate|up of this window into the saved-activation buffers
-            RowMoveParams disp = row_move(c, d, off, limit, nullptr);
+            RowMoveParams disp = row_move(c, whole, d, off, limit, nullptr);
             disp.peers = x_peers;
             disp.row_divisor = d.K;
             QuantOut xo{u8(a->work_x_q), u8(a->work_x_sc), u8(a->x_qt), u8(a->x_sct), d.MB};
-            MOK_TRY(launch_dispatch_quant(disp, xo, false, move_grid(), s));
-            MOK_TRY(mx_gate_up(c, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
+            MOK_TRY(launch_dispatch_quant(disp, xo, false, move_grid(whole), s));
+            MOK_TRY(mx_gate_up(c, whole, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
                                a->w_routed_up_q, a->w_routed_up_sc, a->gate_q, a->gate_sc, a->up_q, a->up_sc,
                                a->work_hidden_q, a->work_hidden_sc, a->hidden_qt, a->hidden_sct, s));
             MOK_TRY(pipe.fork());
         }
         MOK_TRY(pipe.run(m == 0,
-            [&](cudaStream_t st) {     // reverse-combine: w * d_y, quantised in both layouts
-                RowMoveParams rc = row_move(c, d, off, limit, nullptr);
+            [&](cudaStream_t st, const PassCtx& x) {     // reverse-combine: w * d_y, quantised in both layouts
+                RowMoveParams rc = row_move(c, x, d, off, limit, nullptr);
                 rc.peers = dy_peers;
                 rc.scale_peers = rw_peers;
                 rc.row_divisor = d.K;
                 rc.row_scale_out = a->router_weights_routed;
                 QuantOut dyo{u8(a->d_y_q), u8(a->d_y_sc), u8(a->work_d_y_qt), u8(a->work_d_y_sct), d.MB};
-                return launch_dispatch_quant(rc, dyo, true, move_grid(), st);
+                return launch_dispatch_quant(rc, dyo, true, move_grid(x), st);
             },
-            [&](cudaStream_t st) {
+            [&](cudaStream_t st, const PassCtx& x) {
                 {   // d_hidden = d_y @ Wd (weights pre-transposed to [El, I, H]) + SwiGLU backward
-                    MxGemmParams p = mx_base(c, off, limit);
+                    MxGemmParams p = mx_base(c, x, off, limit);
                     p.n_tiles = d.I / kBlockN;
                     p.k_tiles_per_seg = d.H / kMxBlockK;
                     p.b_rows_per_expert = d.I;
@@ -688,11 +777,11 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                     o.a0 = a->d_y_q; o.b0 = a->w_routed_down_T_q;
                     o.a_inner = d.H; o.a_outer = d.MB;
                     o.b_inner = d.H; o.b_outer = static_cast<uint64_t>(d.El) * d.I;
-                    MOK_TRY(launch_mx_gemm(kMxEpiDgradDown, false, o, p, (limit / kBlockM) * p.n_tiles, t_gemm_ctas,
+                    MOK_TRY(launch_mx_gemm(kMxEpiDgradDown, false, o, p, (limit / kBlockM) * p.n_tiles, x.gemm_ctas,
                                            kSlotDgradDownRouted, st));
                 }
                 // d_x = d_gate @ Wg + d_up @ Wu (weights pre-transposed to [El, H, I]) in one accumulator
-                MxGemmParams p = mx_base(c, off, limit);
+                MxGemmParams p = mx_base(c, x, off, limit);
                 p.n_tiles = d.H / kBlockN;
                 p.k_tiles_per_seg = d.I / kMxBlockK;
                 p.num_segs = 2;
@@ -705,24 +794,24 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                 o.a0 = a->d_gate_q; o.a1 = a->d_up_q; o.b0 = a->w_routed_gate_T_q; o.b1 = a->w_routed_up_T_q;
                 o.a_inner = d.I; o.a_outer = d.MB;
                 o.b_inner = d.I; o.b_outer = static_cast<uint64_t>(d.El) * d.H;
-                return launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, t_gemm_ctas, kSlotDgradGateUpRouted, st);
+                return launch_mx_gemm(kMxEpiStore, false, o, p, (limit / kBlockM) * p.n_tiles, x.gemm_ctas, kSlotDgradGateUpRouted, st);
             },
-            [&](cudaStream_t st) {
-                RowMoveParams rd = row_move(c, d, off, limit, a->d_x_routed);
+            [&](cudaStream_t st, const PassCtx& x) {
+                RowMoveParams rd = row_move(c, x, d, off, limit, a->d_x_routed);
                 if (c.defer_combine) return static_cast<int>(MOK_OK);   // mok_bwd_epilogue_rows reads the rows in place
                 rd.peers = dxr_peers;
                 rd.scale_peers = drw_peers;
                 rd.partials = a->d_router_weight_partials;
                 rd.partial_cols = 4 * partial_cols   /* the MXFP8 epilogue writes one partial per 64-column slice */;
-                return launch_combine_rows(rd, move_grid(), st);
+                return launch_combine_rows(rd, move_grid(x), st);
             }));
         MOK_TRY(pipe.join());
         const int acc = m > 0 ? 1 : 0;
-        MOK_TRY(mx_wgrad(c, d, off, limit, a->work_d_y_qt, a->work_d_y_sct, d.H, a->hidden_qt, a->hidden_sct, d.I,
+        MOK_TRY(mx_wgrad(c, whole, d, off, limit, a->work_d_y_qt, a->work_d_y_sct, d.H, a->hidden_qt, a->hidden_sct, d.I,
                          a->d_w_routed_down, acc, s));
-        MOK_TRY(mx_wgrad(c, d, off, limit, a->work_d_gate_qt, a->work_d_gate_sct, d.I, a->x_qt, a->x_sct, d.H,
+        MOK_TRY(mx_wgrad(c, whole, d, off, limit, a->work_d_gate_qt, a->work_d_gate_sct, d.I, a->x_qt, a->x_sct, d.H,
                          a->d_w_routed_gate, acc, s));
-        MOK_TRY(mx_wgrad(c, d, off, limit, a->work_d_up_qt, a->work_d_up_sct, d.I, a->x_qt, a->x_sct, d.H,
+        MOK_TRY(mx_wgrad(c, whole, d, off, limit, a->work_d_up_qt, a->work_d_up_sct, d.I, a->x_qt, a->x_sct, d.H,
                          a->d_w_routed_up, acc, s));
     }
     return MOK_OK;

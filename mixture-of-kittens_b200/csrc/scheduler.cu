@@ -12,6 +12,8 @@
 //   pass 3  every block rebuilds expert bases from cnt; one warp per chunk walks its routes in
 //           order, ranks equal experts inside the warp with match.any, and writes the slots.
 // Algorithmic traffic: 2 * W*T*K*4 B of route reads + 2 * capacity * 4 B of table writes.
+#include <atomic>
+
 #include "common.cuh"
 #include "profile.cuh"
 
@@ -236,8 +238,19 @@ int launch_schedule(const int32_t* topk_all, int ep_size, int num_local_tokens, 
     const int chunk_blocks = (ep_size * kChunks + kWarpsPerBlock - 1) / kWarpsPerBlock;
     const size_t smem_count = static_cast<size_t>(kWarpsPerBlock) * p.El * sizeof(int);
     const size_t smem_place = (static_cast<size_t>(p.El) * p.W + p.El + static_cast<size_t>(kWarpsPerBlock) * p.El) * sizeof(int);
-    MOK_CUDA_CHECK(cudaFuncSetAttribute(sched_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_count)));
-    MOK_CUDA_CHECK(cudaFuncSetAttribute(sched_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_place)));
+    // The dynamic shared-memory ceiling is a sticky per-device attribute: set it once to what the largest accepted
+    // problem needs, so that concurrent calls with different expert counts cannot lower it under one another.
+    static std::atomic<bool> configured[64];
+    int dev = 0;
+    MOK_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !configured[dev].load(std::memory_order_acquire)) {
+        constexpr size_t kMaxCount = static_cast<size_t>(kWarpsPerBlock) * MOK_MAX_LOCAL_EXPERTS * sizeof(int);
+        constexpr size_t kMaxPlace = (static_cast<size_t>(MOK_MAX_LOCAL_EXPERTS) * MOK_MAX_PEERS + MOK_MAX_LOCAL_EXPERTS +
+                                      static_cast<size_t>(kWarpsPerBlock) * MOK_MAX_LOCAL_EXPERTS) * sizeof(int);
+        MOK_CUDA_CHECK(cudaFuncSetAttribute(sched_count_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kMaxCount)));
+        MOK_CUDA_CHECK(cudaFuncSetAttribute(sched_place_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kMaxPlace)));
+        if (dev >= 0 && dev < 64) configured[dev].store(true, std::memory_order_release);
+    }
     ProfScope prof(kSlotScheduler, stream, 3);
     sched_count_kernel<<<chunk_blocks, kBlockThreads, smem_count, stream>>>(p);
     const int pair_blocks = (p.El * p.W + kWarpsPerBlock - 1) / kWarpsPerBlock;
@@ -288,19 +301,19 @@ namespace mok {
 namespace {
 constexpr size_t kStaticScratchBytes = 4u << 20;   // enough for ep_size * num_local_experts <= 4080
 static __device__ __align__(256) unsigned char g_static_sched_scratch[kStaticScratchBytes];
-void* g_static_scratch_addr[64] = {nullptr};
+std::atomic<void*> g_static_scratch_addr[64];    // per device; two threads that race on the first call store the same address
 
 int static_scratch_for_current_device(void** out) {
     int dev = -1;
     MOK_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return MOK_ERR_UNSUPPORTED;
-    if (g_static_scratch_addr[dev] == nullptr) {
-        void* ptr = nullptr;
+    void* ptr = g_static_scratch_addr[dev].load(std::memory_order_acquire);
+    if (ptr == nullptr) {
         const cudaError_t err = cudaGetSymbolAddress(&ptr, g_static_sched_scratch);
-        if (err != cudaSuccess || ptr == nullptr) return MOK_ERR_CUDA;
-        g_static_scratch_addr[dev] = ptr;
+        if (err != cudaSuccess || ptr == nullptr) { note_cuda_error(err, __FILE__, __LINE__); return MOK_ERR_CUDA; }
+        g_static_scratch_addr[dev].store(ptr, std::memory_order_release);
     }
-    *out = g_static_scratch_addr[dev];
+    *out = ptr;
     return MOK_OK;
 }
 }  // namespace

@@ -150,6 +150,17 @@ mok_profile_collect = _sig("mok_profile_collect", C.c_int, [C.POINTER(C.c_double
 mok_gemm_bf16 = _sig("mok_gemm_bf16", C.c_int, [vp, vp, vp, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, vp, vp])
 
 
+class WorkspaceBytes(C.Structure):
+    _fields_ = [("schedule_capacity", C.c_int64)] + [(n, C.c_size_t) for n in (
+        "x_buffer combine_buffer d_y_buffer d_x_routed_buffer router_weight_buffer d_router_weight_buffer "
+        "all_gather_top_experts_buffer barrier_buffer barrier_target status_word schedule_tables schedule_scratch").split()]
+
+
+mok_query_workspace_bytes = _sig("mok_query_workspace_bytes", C.c_int,
+                                 [C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_double, C.POINTER(WorkspaceBytes)])
+mok_last_status = _sig("mok_last_status", C.c_int, [vp, C.POINTER(C.c_int32), C.c_int, vp])
+
+
 def check(rc: int, what: str) -> None:
     """Turns a negative return code of the C ABI into a Python exception."""
     if rc == 0:
@@ -192,10 +203,10 @@ def last_status(device: torch.device | None = None, clear: bool = False) -> tupl
     """Reads the status word of `device` (synchronises).  Returns (code, detail, block)."""
     device = device or torch.device("cuda", torch.cuda.current_device())
     t = status_tensor(device)
-    code, detail, block, _ = t.tolist()
-    if clear:
-        t.zero_()
-    return code, detail, block
+    out = (C.c_int32 * 4)()
+    with torch.cuda.device(device):
+        check(mok_last_status(t.data_ptr(), out, 1 if clear else 0, stream_ptr(device)), "last_status")
+    return int(out[0]), int(out[1]), int(out[2])
 
 
 def raise_for_status(device: torch.device | None = None) -> None:

@@ -46,6 +46,30 @@ def test_host_detected_argument_errors():
     assert L.mok_fwd_epilogue_rows(None, None, None, None, None, None, None, None, 512, 256, 2, 4096, None) == -1
     assert L.mok_bwd_epilogue_rows(None, None, None, 4, None, None, None, None, None, None, 512, 256, 2, 4096, None) == -1
     assert L.mok_last_cuda_error() == b""
+    assert L.mok_last_status(None, None, 0, None) == -1
+
+
+def test_query_workspace_bytes():
+    """The size query follows the reference's capacity formula T*K*max(2, ceil(W*multiplier)) and buffer shapes."""
+    import mok
+    L = mok._lib
+    wb = L.WorkspaceBytes()
+    assert L.mok_query_workspace_bytes(8, 16384, 7168, 8, 32, 0.5, wb) == 0
+    R = 16384 * 8
+    assert wb.schedule_capacity == R * 4
+    assert wb.x_buffer == wb.d_y_buffer == 16384 * 7168 * 2
+    assert wb.combine_buffer == wb.d_x_routed_buffer == R * 7168 * 2
+    assert wb.router_weight_buffer == wb.d_router_weight_buffer == R * 4
+    assert wb.all_gather_top_experts_buffer == 8 * R * 4
+    assert (wb.barrier_buffer, wb.barrier_target, wb.status_word) == (4, 4, 16)
+    assert wb.schedule_tables == 2 * 4 * R * 4 + 4 + 32 * 4
+    assert wb.schedule_scratch == L.mok_schedule_scratch_bytes(8, 32)
+    assert L.mok_query_workspace_bytes(1, 512, 256, 2, 4, 1.0, wb) == 0 and wb.schedule_capacity == 512 * 2 * 2
+    assert L.mok_query_workspace_bytes(8, 16384, 7168, 8, 32, 1.0, wb) == 0 and wb.schedule_capacity == R * 8
+    for bad in ((0, 512, 256, 2, 4, 1.0), (9, 512, 256, 2, 4, 1.0), (1, 500, 256, 2, 4, 1.0), (1, 512, 100, 2, 4, 1.0),
+                (1, 512, 256, 0, 4, 1.0), (1, 512, 256, 2, 0, 1.0), (1, 512, 256, 2, 4, 0.0)):
+        assert L.mok_query_workspace_bytes(*bad, wb) == -1, bad
+    assert L.mok_query_workspace_bytes(1, 512, 256, 2, 4, 1.0, None) == -1
 
 
 def test_struct_sizes_match_header():
@@ -53,7 +77,7 @@ def test_struct_sizes_match_header():
     import subprocess
     import tempfile
     import mok
-    src = '#include <stdio.h>\n#include "mok_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu", sizeof(mok_layer_common), sizeof(mok_fwd_bf16_args), sizeof(mok_bwd_bf16_args), sizeof(mok_fwd_mxfp8_args), sizeof(mok_bwd_mxfp8_args));return 0;}\n'
+    src = '#include <stdio.h>\n#include "mok_b200.h"\nint main(){printf("%zu %zu %zu %zu %zu %zu", sizeof(mok_layer_common), sizeof(mok_fwd_bf16_args), sizeof(mok_bwd_bf16_args), sizeof(mok_fwd_mxfp8_args), sizeof(mok_bwd_mxfp8_args), sizeof(mok_workspace_bytes));return 0;}\n'
     with tempfile.TemporaryDirectory() as d:
         c = os.path.join(d, "s.c")
         open(c, "w").write(src)
@@ -62,7 +86,7 @@ def test_struct_sizes_match_header():
         sizes = [int(v) for v in subprocess.check_output([exe]).split()]
     L = mok._lib
     assert sizes == [ctypes.sizeof(L.LayerCommon), ctypes.sizeof(L.FwdBf16Args), ctypes.sizeof(L.BwdBf16Args),
-                     ctypes.sizeof(L.FwdMxfp8Args), ctypes.sizeof(L.BwdMxfp8Args)]
+                     ctypes.sizeof(L.FwdMxfp8Args), ctypes.sizeof(L.BwdMxfp8Args), ctypes.sizeof(L.WorkspaceBytes)]
 
 
 def test_ctypes_field_order_matches_header():
@@ -72,8 +96,8 @@ def test_ctypes_field_order_matches_header():
     text = re.sub(r"/\*.*?\*/", "", open(os.path.join(ROOT, "include", "mok_b200.h")).read(), flags=re.S)
     pairs = (("mok_layer_common", L.LayerCommon), ("mok_fwd_bf16_args", L.FwdBf16Args),
              ("mok_bwd_bf16_args", L.BwdBf16Args), ("mok_fwd_mxfp8_args", L.FwdMxfp8Args),
-             ("mok_bwd_mxfp8_args", L.BwdMxfp8Args))
-    type_words = {"const", "void", "uint64_t", "int32_t", "int", "float", "mok_layer_common"}
+             ("mok_bwd_mxfp8_args", L.BwdMxfp8Args), ("mok_workspace_bytes", L.WorkspaceBytes))
+    type_words = {"const", "void", "uint64_t", "int32_t", "int64_t", "size_t", "int", "float", "mok_layer_common"}
     for cname, struct in pairs:
         body = re.search(r"typedef struct %s \{(.*?)\} %s;" % (cname, cname), text, re.S).group(1)
         names = [w for decl in body.split(";") for w in decl.replace("*", " ").replace(",", " ").split()
