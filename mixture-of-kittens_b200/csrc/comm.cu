@@ -114,12 +114,13 @@ __global__ void __launch_bounds__(256) invert_rows_kernel(const int* __restrict_
 
 // same arithmetic as epilogue_kernel, but the k-th routed row of token t is rows[route_row[t*K+k]]
 // (a route without a row adds nothing); kWeighted = forward, else backward, which also sums each
-// route's router-gradient partials in column order
+// route's router-gradient partials in column order.  `out` may be `shared_rows` itself (the backward pass
+// sums in place: every element is read by the thread that writes it, before it writes), so neither is restrict.
 template <bool kWeighted>
-__global__ void __launch_bounds__(256) epilogue_rows_kernel(const uint4* __restrict__ shared_rows, const uint4* __restrict__ rows,
+__global__ void __launch_bounds__(256) epilogue_rows_kernel(const uint4* shared_rows, const uint4* __restrict__ rows,
                                                             const int* __restrict__ route_row, const float* __restrict__ weights,
                                                             const float* __restrict__ partials, int partial_cols,
-                                                            float* __restrict__ d_router_weights, uint4* __restrict__ out,
+                                                            float* __restrict__ d_router_weights, uint4* out,
                                                             int64_t T, int vec_per_row, int K) {
     const int64_t total = T * vec_per_row;
     const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;

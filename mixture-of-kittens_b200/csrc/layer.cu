@@ -353,6 +353,10 @@ int move_grid(const PassCtx& x) {
     return configured > 0 ? configured : device_sm_count() * 4;
 }
 
+// the quantising dispatch is arithmetic-heavy and its CTAs are small (33 KB of shared memory, 256 threads): six of
+// them fill a dedicated SM, and they do not fit beside an MXFP8 GEMM CTA, so they stay on the SMs set aside
+int quant_grid(const PassCtx& x) { return x.comm_sms > 0 ? x.comm_sms * 6 : move_grid(x); }
+
 int pipeline_chunks(const mok_layer_common& c, int limit) {
     static const int configured = [] { const int v = env_int("MOK_B200_CHUNKS", 0); return v < 0 ? 0 : (v > 32 ? 32 : v); }();
     // default: no chunking on a single rank (movement and GEMMs compete for HBM there), four chunks
@@ -678,7 +682,7 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
                 disp.peers = x_peers;
                 disp.row_divisor = d.K;
                 QuantOut xo{u8(a->work_x_q), u8(a->work_x_sc), u8(a->x_qt), u8(a->x_sct), d.MB};
-                return launch_dispatch_quant(disp, xo, false, move_grid(x), st);
+                return launch_dispatch_quant(disp, xo, false, quant_grid(x), st);
             },
             [&](cudaStream_t st, const PassCtx& x) {
                 MOK_TRY(mx_gate_up(c, x, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
@@ -739,7 +743,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
             disp.peers = x_peers;
             disp.row_divisor = d.K;
             QuantOut xo{u8(a->work_x_q), u8(a->work_x_sc), u8(a->x_qt), u8(a->x_sct), d.MB};
-            MOK_TRY(launch_dispatch_quant(disp, xo, false, move_grid(whole), s));
+            MOK_TRY(launch_dispatch_quant(disp, xo, false, quant_grid(whole), s));
             MOK_TRY(mx_gate_up(c, whole, d, off, limit, a->work_x_q, a->work_x_sc, a->w_routed_gate_q, a->w_routed_gate_sc,
                                a->w_routed_up_q, a->w_routed_up_sc, a->gate_q, a->gate_sc, a->up_q, a->up_sc,
                                a->work_hidden_q, a->work_hidden_sc, a->hidden_qt, a->hidden_sct, s));
@@ -753,7 +757,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                 rc.row_divisor = d.K;
                 rc.row_scale_out = a->router_weights_routed;
                 QuantOut dyo{u8(a->d_y_q), u8(a->d_y_sc), u8(a->work_d_y_qt), u8(a->work_d_y_sct), d.MB};
-                return launch_dispatch_quant(rc, dyo, true, move_grid(x), st);
+                return launch_dispatch_quant(rc, dyo, true, quant_grid(x), st);
             },
             [&](cudaStream_t st, const PassCtx& x) {
                 {   // d_hidden = d_y @ Wd (weights pre-transposed to [El, I, H]) + SwiGLU backward

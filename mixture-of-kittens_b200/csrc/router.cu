@@ -36,7 +36,8 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_topk_kernel(const fl
 #pragma unroll
         for (int j = 0; j < kPerLane; ++j) {
             const int e = lane + 32 * j;
-            v[j] = e < E ? row[e] : -INFINITY;
+            const float lv = e < E ? row[e] : -INFINITY;
+            v[j] = lv == lv ? lv : -INFINITY;       // a NaN logit ranks with -inf: it wins only when nothing else is left
         }
         unsigned taken = 0;                // bit j: this lane's j-th value has been selected
         float my_val = -INFINITY;          // lane k keeps the k-th selected (value, expert)
@@ -48,7 +49,7 @@ __global__ void __launch_bounds__(kRouterWarps * 32) router_topk_kernel(const fl
             for (int j = 0; j < kPerLane; ++j) {
                 const int e = lane + 32 * j;
                 const bool free_slot = e < E && !((taken >> j) & 1u);
-                // NaNs never win; among equal values the lower expert index wins
+                // among equal values the lower expert index wins; the first free slot seeds the search
                 if (free_slot && (v[j] > best || (v[j] == best && e < best_e) || best_e == 0x7fffffff)) { best = v[j]; best_e = e; }
             }
 #pragma unroll

@@ -772,10 +772,10 @@ def router_topk_bwd(top_experts: Tensor, router_weights: Tensor, d_router_weight
         _need(t.dtype == torch.float32, f"{name} must have dtype torch.float32", TypeError)
     _need(type(num_experts) is int and K <= num_experts <= 1024 and K <= 32, "num_experts must be in [topk, 1024]")
     idx = top_experts.to(torch.int32).contiguous()
+    rw, d_rw = router_weights.contiguous(), d_router_weights.contiguous()     # kept alive until the launch is enqueued
     d_logits = torch.empty(T, num_experts, dtype=torch.float32, device=top_experts.device)
-    _lib.check(_lib.mok_router_topk_bwd(idx.data_ptr(), router_weights.contiguous().data_ptr(),
-                                        d_router_weights.contiguous().data_ptr(), d_logits.data_ptr(), T, num_experts, K,
-                                        _lib.stream_ptr(top_experts.device)), "router_topk_bwd")
+    _lib.check(_lib.mok_router_topk_bwd(idx.data_ptr(), rw.data_ptr(), d_rw.data_ptr(), d_logits.data_ptr(), T,
+                                        num_experts, K, _lib.stream_ptr(top_experts.device)), "router_topk_bwd")
     return d_logits
 
 

@@ -140,6 +140,42 @@ def main():
         failures.append(f"torch baseline vs kernels: output rel-L2 {e:.3e}")
     if mok.last_status(dev)[0] != 0:
         failures.append(f"router/baseline section: status {mok.last_status(dev)}")
+    F.clear_workspace_cache()
+    # Two cases with the hidden / intermediate sizes, expert counts and top-k of the full-size training workloads
+    # (BF16: H=4096, I=1536, 64 experts, top-6; MXFP8: H=7168, I=2048, 32 experts per rank, top-8) on fewer
+    # tokens, windows cut into chunks with SMs set aside for the row movers.  The CPU oracle would take minutes at
+    # these sizes, so sampled tokens are recomputed in fp32 on the device (bench.sampled_parity, itself pinned to
+    # the oracle by a CPU test); every routed row of a sampled token comes back from the rank that owns its expert.
+    shaped = [("bf16 H=4096", dict(T=1024, H=4096, I=1536, E=64, K=6, router="uniform", backward=True, minibatch=256,
+                                   macrobatch=131072, multiplier=1.0), 24, 1e-2),
+              ("mxfp8 H=7168", dict(T=512, H=7168, I=2048, E=32 * world, K=8, router="linear", backward=True, mxfp8=True,
+                                    minibatch=256, macrobatch=131072, multiplier=1.0), 8, 3e-2)]
+    for label, wl, samples, tol in shaped:
+        run = bench.LayerRun(label, wl, rank, world, local, dist.group.WORLD)
+        results = {}
+        for n_sms in (None, 4, 52):                  # the configuration's default, the smallest and the largest swept
+            if n_sms is not None:
+                run.set_comm_sms(n_sms)
+            out, grads, sched_s, ctx_s = run.step(keep=True)
+            torch.cuda.synchronize()
+            if n_sms is None:
+                par = bench.sampled_parity(wl, rank, world, dev, run.dev_in, out, grads, sched_s, ctx_s, samples)
+                for name, e in par.items():
+                    worst = max(worst, e)
+                    if not e < tol:
+                        failures.append(f"{label}: {name} rel-L2 {e:.3e}")
+            results[n_sms] = (out, grads)
+            del sched_s, ctx_s
+        for n_sms in (4, 52):
+            same = torch.equal(results[None][0], results[n_sms][0]) and all(
+                torch.equal(a, b) for a, b in zip(results[None][1], results[n_sms][1]))
+            if not same:
+                failures.append(f"{label}: results with {n_sms} communication SMs differ bitwise from the default")
+        if mok.last_status(dev)[0] != 0:
+            failures.append(f"{label}: status {mok.last_status(dev)}")
+        del results
+        run.release()
+        F.clear_workspace_cache()
     flag = torch.tensor([len(failures)], device=dev)
     dist.all_reduce(flag)
     print(json.dumps({"rank": rank, "world": world, "worst_rel_l2": worst, "failures": failures}), flush=True)

@@ -158,3 +158,69 @@ def test_added_operators_and_wrappers():
     assert mok.ops.SELF_PTRS == [-1]
     assert callable(mok.nn.moe_experts) and issubclass(mok.nn.MoKLayer, torch.nn.Module)
     assert callable(mok.functional.route) and callable(mok.functional.route_and_schedule)
+
+
+# ------------------------------------------------------------------------------------------
+# bench.py helpers that run without a GPU
+# ------------------------------------------------------------------------------------------
+def test_bench_mx_emulation_matches_the_oracle_quantiser():
+    """bench.py checks MXFP8 runs against an fp32 recomputation whose operands go through a block
+    quantise-dequantise written with torch ops; it must be the oracle's quantiser bit for bit."""
+    import torch
+    import bench
+    from oracle import mok_oracle as O
+    g = torch.Generator().manual_seed(1)
+    t = (torch.randn(64, 256, generator=g) * torch.exp(torch.randn(64, 1, generator=g) * 4)).to(torch.bfloat16).float()
+    t[3] = 0
+    t[5, :32] = 0
+    t[7] = 448.0
+    t[8] = 2.0 ** -20
+    t[9, :32] = torch.tensor([448.0 * 2.0 ** k for k in range(-16, 16)]).to(torch.bfloat16).float()
+    for axis in (0, 1):
+        assert torch.equal(bench.mx_quant_dequant(t, axis), O._mx(t, axis)), axis
+
+
+def test_bench_traffic_model_and_roofline_fractions():
+    import bench
+    full = bench.dominant_traffic("C2", 128, 145664)
+    assert full == 6291456 * 128 + 8322 * 145664
+    assert bench.dominant_traffic("C4", 32, 1000) is None            # no capture on file: the line prints null
+    wl = bench.WORKLOADS["C2"]
+    res = {"prof": {"gemm_gate_up_swiglu_routed": (66.18, 100)}, "n_rows": 145664}
+    roof = bench.roofline_record("C2", wl, res, 100, 1)
+    assert abs(roof["achieved"] - 4 * 16384 * 8 * 2048 * 768 / 0.6618e-3 / 1e12) < 1e-6
+    assert roof["frac_vs_burst"] < roof["frac_vs_sustained"]
+    short = bench.finish_roofline(dict(roof), 0.07, {"reasons": []})
+    assert short["peak"] == roof["burst_peak"] and short["frac"] == roof["frac_vs_burst"]
+    capped = bench.finish_roofline(dict(roof), 0.07, {"reasons": ["sw_power_cap"]})
+    assert capped["peak"] == roof["sustained_peak"]
+    long_run = bench.finish_roofline(dict(roof), 3.0, {"reasons": []})
+    assert long_run["frac"] == roof["frac_vs_sustained"]
+
+
+def test_bench_sampled_check_is_pinned_to_the_oracle():
+    """bench.py's after-run parity check recomputes sampled tokens on its own; fed with the oracle's results for
+    the same seeded two-rank inputs it must report (almost) no error, in BF16 and in MXFP8 arithmetic."""
+    import types
+    import torch
+    import bench
+    from oracle import mok_oracle as O
+    cpu = torch.device("cpu")
+    for mx in (False, True):
+        wl = dict(T=512, H=256, I=256, E=8, K=3, router="linear", backward=True, mxfp8=mx)
+        W = 2
+        raw = [bench.make_inputs(wl, p, W, cpu, pinned=False) for p in range(W)]
+        ranks = [O.RankInputs(x=s["x"], topk_experts=s["topk"], router_weights=s["rw"], w_shared_gate=prm[0],
+                              w_shared_up=prm[1], w_shared_down=prm[2], w_routed_gate=prm[3], w_routed_up=prm[4],
+                              w_routed_down=prm[5], d_output=s["d_out"]) for s, prm in raw]
+        ref = O.layer_forward_backward(ranks, device_rounding=True, mxfp8=mx)
+        for rank in range(W):
+            r = ref[rank]
+            sched = types.SimpleNamespace(tokens_per_expert=torch.from_numpy(r["tokens_per_expert"]),
+                                          peer_rank=torch.from_numpy(r["peer_rank"]),
+                                          peer_token_idx=torch.from_numpy(r["peer_token_idx"]))
+            grads = (r["d_x"], r["d_router_weights"])
+            got = bench.sampled_parity(wl, rank, W, cpu, raw[rank][0], r["output"], grads, sched, None, 16)
+            assert set(got) == {"output", "d_x", "d_router_weights"}
+            for name, err in got.items():
+                assert err < 3e-3, (mx, rank, name, err)

@@ -207,3 +207,42 @@ def test_gemm_mxfp8(cuda_device, m, n, k):
     assert mok.last_status(cuda_device)[0] == 0
     assert torch.isfinite(c.float()).all()
     assert rel_l2(ref, c.float()) < 4e-3
+
+
+# ----------------------------------------------------------------------------------------
+# device barrier: the bounded wait runs out, reports it and returns
+# ----------------------------------------------------------------------------------------
+def test_barrier_wait_runs_out_and_recovers(cuda_device):
+    """A two-rank barrier whose second "rank" never arrives: the peer list is {own counter, a scratch word}, so
+    the own counter reaches 1 of the 2 arrivals it waits for.  With a 2 ms limit the kernel must give up, write
+    MOK_STATUS_BARRIER_TIMEOUT (detail = the counter value it saw) and return; the context stays usable and a
+    one-rank barrier on a fresh counter completes.  (The reference spins without limit here,
+    csrc/utils.cuh:291-293.)"""
+    import time
+    mok = _mok()
+    L = mok._lib
+    dev = cuda_device
+    mok.last_status(dev, clear=True)
+    counter = torch.zeros(1, dtype=torch.int32, device=dev)
+    scratch = torch.zeros(1, dtype=torch.int32, device=dev)
+    target = torch.zeros(1, dtype=torch.int32, device=dev)
+    status = L.status_tensor(dev)
+    t0 = time.perf_counter()
+    L.check(L.mok_barrier_all(counter.data_ptr(), L.ptr_array([counter.data_ptr(), scratch.data_ptr()]), 2,
+                              target.data_ptr(), status.data_ptr(), 2_000_000, L.stream_ptr(dev)), "barrier_all")
+    torch.cuda.synchronize()
+    assert time.perf_counter() - t0 < 2.0                       # it gave up after milliseconds, not the default minutes
+    code, detail, _block = mok.last_status(dev, clear=True)
+    assert code == 2 and detail == 1, (code, detail)
+    assert int(target.item()) == 2 and int(counter.item()) == 1 and int(scratch.item()) == 1
+    # a one-rank barrier on fresh state passes
+    fresh, fresh_target = torch.zeros(1, dtype=torch.int32, device=dev), torch.zeros(1, dtype=torch.int32, device=dev)
+    L.check(L.mok_barrier_all(fresh.data_ptr(), L.ptr_array([fresh.data_ptr()]), 1, fresh_target.data_ptr(),
+                              status.data_ptr(), 2_000_000, L.stream_ptr(dev)), "barrier_all")
+    torch.cuda.synchronize()
+    assert mok.last_status(dev)[0] == 0
+    assert int(fresh.item()) == 1 and int(fresh_target.item()) == 1
+    status.copy_(torch.tensor([2, 1, 0, 0], dtype=torch.int32))     # what a caller sees at its step boundary
+    with pytest.raises(mok._lib.MokNativeError):
+        mok.raise_for_status(dev)
+    mok.last_status(dev, clear=True)

@@ -89,6 +89,53 @@ def test_multiple_macrobatches_replay(cuda_device, single_rank_group):
         assert rel_l2(ref[name].float(), many[name].float()) < BF16_REL_L2, name
 
 
+@pytest.mark.parametrize("macrobatch", [131072, 512])
+@pytest.mark.parametrize("mxfp8", [False, True])
+def test_expert_without_routes(cuda_device, single_rank_group, mxfp8, macrobatch):
+    """One local expert receives no route at all: its three weight-gradient slabs must be exact zeros
+    (the reference zeroes them in a pass of its own, csrc/utils.cuh:17-34), with one window and with
+    several (accumulating weight gradients must not skip the first store)."""
+    import dataclasses
+    cfg = dict(T=1024, H=256, I=256, E=4, W=1, K=2)
+    inp = O.make_rank_inputs(0, seed=31, **cfg)
+    g = torch.Generator().manual_seed(77)
+    allowed = torch.tensor([0, 1, 3])                     # expert 2 is never chosen; a token's two experts differ
+    pick = torch.stack([torch.randperm(3, generator=g)[:2] for _ in range(cfg["T"])])
+    inp = dataclasses.replace(inp, topk_experts=allowed[pick].to(torch.int64))
+    ref = O.layer_forward_backward([inp], device_rounding=True, mxfp8=mxfp8)[0]
+    got = run_layer(cuda_device, single_rank_group, inp, mxfp8=mxfp8, macrobatch=macrobatch)
+    assert int(got["schedule"].tokens_per_expert[2].item()) == 0
+    tol = MXFP8_REL_L2 if mxfp8 else BF16_REL_L2
+    assert rel_l2(ref["output"].float(), got["output"].float()) < tol
+    for name in GRAD_NAMES:
+        assert rel_l2(ref[name].float(), got[name].float()) < tol, name
+    for name in ("d_w_routed_gate", "d_w_routed_up", "d_w_routed_down"):
+        assert not bool(got[name][2].any()), name
+        assert bool(got[name][0].any()), name
+
+
+@pytest.mark.parametrize("topk,experts", [(9, 16), (55, 64)])
+def test_large_and_odd_topk(cuda_device, single_rank_group, topk, experts):
+    """Odd top-k and the reference's largest tested top-k (55, tests/test_ops.py:1608-1803 there): the forward
+    output and d_x are sums over that many routed rows per token.  Checked on the fast path (rows gathered through
+    the schedule) and on the combine-buffer path, which must agree bit for bit."""
+    import mok
+    cfg = dict(T=512, H=256, I=256, E=experts, W=1, K=topk)
+    inp = O.make_rank_inputs(0, seed=3 + topk, **cfg)
+    ref = O.layer_forward_backward([inp], device_rounding=True)[0]
+    fast = run_layer(cuda_device, single_rank_group, inp, multiplier=2.0)
+    for name in ("output",) + GRAD_NAMES:
+        assert rel_l2(ref[name].float(), fast[name].float()) < BF16_REL_L2, name
+    saved = mok.functional.SINGLE_RANK_FAST_PATH
+    mok.functional.SINGLE_RANK_FAST_PATH = False
+    try:
+        slow = run_layer(cuda_device, single_rank_group, inp, multiplier=2.0)
+    finally:
+        mok.functional.SINGLE_RANK_FAST_PATH = saved
+    for name in ("output",) + GRAD_NAMES:
+        assert torch.equal(fast[name], slow[name]), name
+
+
 @pytest.mark.parametrize("mxfp8", [False, True])
 def test_single_rank_fast_path_is_bit_identical(cuda_device, single_rank_group, monkeypatch, mxfp8):
     """Gathering the routed rows in the epilogue (no staging copies, barriers or combine pass) gives the bytes
@@ -128,7 +175,7 @@ def test_saved_activations_match_oracle(cuda_device, single_rank_group):
 
 
 def test_full_size_forward_sampled(cuda_device, single_rank_group):
-    """BASELINE config 2 shape (T=16384, H=2048, 128 experts, top-8, I=768): the oracle is too
+    """The full single-GPU forward shape (T=16384, H=2048, 128 experts, top-8, I=768): the oracle is too
     slow for every token, so 48 sampled tokens are recomputed in fp32 on the CPU oracle path."""
     cfg = dict(T=16384, H=2048, I=768, E=128, W=1, K=8)
     inp = O.make_rank_inputs(0, seed=0, with_grad=False, **cfg)
@@ -151,7 +198,7 @@ def test_full_size_forward_sampled(cuda_device, single_rank_group):
 
 
 def test_full_size_backward_sampled(cuda_device, single_rank_group):
-    """One rank's share of BASELINE config 3 at EP=8 with every route local (T=16384, H=4096, 8 experts, top-6,
+    """One rank's share of the eight-rank BF16 training shape with every route local (T=16384, H=4096, 8 experts, top-6,
     I=1536), forward + backward.  The oracle is too slow for every token, so d_x and d_router_weights of 24 sampled
     tokens are recomputed in fp32 with the device's bf16 rounding points, and sampled rows of the shared-expert
     weight gradients are contracted over all tokens from the saved activations."""
@@ -193,7 +240,7 @@ def test_full_size_backward_sampled(cuda_device, single_rank_group):
 
 
 def test_full_size_mxfp8_share_is_deterministic_and_close_to_bf16(cuda_device, single_rank_group):
-    """A quarter of one rank's share of BASELINE config 4 (H=7168, I=2048, 16 of the 32 local experts, top-8, 4096 tokens):
+    """A quarter of one rank's share of the eight-rank MXFP8 training shape (H=7168, I=2048, 16 of the 32 local experts, top-8, 4096 tokens):
     MXFP8 forward + backward twice bit-identically, and within the reference's own MXFP8-vs-BF16 bound
     (sum|d| / sum|ref| <= 0.1, tests/utils.py:8) of the BF16 run on the same inputs."""
     cfg = dict(T=4096, H=7168, I=2048, E=16, W=1, K=8)

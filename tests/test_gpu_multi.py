@@ -1,6 +1,6 @@
 """GPU, 2+ devices: expert-parallel parity.  Spawns one process per GPU with torch.distributed.run
 and checks every rank against the multi-rank CPU oracle (tests/ep_worker.py).  Skipped on a
-single-GPU box; the round's multi-GPU runs call the worker directly."""
+single-GPU box."""
 import os
 import subprocess
 import sys
