@@ -48,7 +48,11 @@ __host__ __device__ constexpr int mx_stages(int epi, bool k2) { return k2 ? (epi
 __host__ __device__ constexpr int mx_tile_bytes(bool k2) { return kMxABytes + (k2 ? kMxBBytes / 2 : kMxBBytes); }
 constexpr int kMxEpiGroups = 4;                       // epilogue warps per TMEM lane quarter (each takes 64 of the 256 columns)
 constexpr int kMxEpiWarps = 4 * kMxEpiGroups;
-constexpr int kMxThreads = 64 + 32 * kMxEpiWarps;     // producer warp, MMA warp, sixteen epilogue warps
+constexpr int kMxThreads = 128 + 32 * kMxEpiWarps;    // warps 0-3: producer, MMA issuer, two spare; warps 4-19: epilogue
+// Registers are re-balanced between the roles with setmaxnreg (it works on groups of four warps, hence the two spare
+// warps): the kernel starts with 96 registers per thread (five warps share each of the SM's four register files), the
+// first group gives up half of its share and the sixteen epilogue warps grow to 112.
+constexpr int kMxLightRegs = 48, kMxEpiRegs = 112;
 constexpr int kMxTrBytes = kMxEpiWarps * 32 * 17 * 4; // per-epilogue-warp transpose tiles
 __host__ __device__ constexpr int mx_smem_bytes(int epi, bool k2) {
     return mx_stages(epi, k2) * (mx_tile_bytes(k2) + kMxSfBytes) + 256 + kMaxExperts * 4 + (epi == 0 ? 0 : kMxTrBytes) + 1024;
@@ -226,6 +230,8 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         }
     };
 
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kMxLightRegs));
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
@@ -336,15 +342,17 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 else { mbar_arrive(tfull_bar); if (k2) mbar_arrive_cta(tfull_bar, 1); }
             }
         }
+    }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kMxEpiRegs));
         // ------------------------------------------------------------------ epilogue warps
         // Sixteen warps: four per TMEM lane quarter (a warp may only read lanes 32*(warp%4)...), each taking
-        // 64 of the tile's 256 columns, so a thread holds its share of the accumulator as 32 packed words and
-        // nothing spills.  More resident warps also hide the latency of the epilogue's loads and stores.
+        // 64 of the tile's 256 columns, so a thread holds its share of the accumulator as 32 packed words.
+        // More resident warps also hide the latency of the epilogue's loads and stores.
         const int quarter = warp & 3;
-        const int sub = (warp - 2) >> 2;                 // 0..3
+        const int sub = (warp - 4) >> 2;                 // 0..3
         const int r_in_tile = quarter * 32 + lane;
-        uint32_t* tr = tr_smem + (warp - 2) * kMxTrWords;
+        uint32_t* tr = tr_smem + (warp - 4) * kMxTrWords;
         int it = 0;
         bool ok = true;
         for (int tile = tile_first; tile < num_tiles && ok; tile += tile_step, ++it) {
@@ -353,7 +361,30 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
             if (!mbar_wait(tfull_bar, it & 1, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16);
-            uint32_t pk[32];
+            const size_t row = static_cast<size_t>(m_idx) * kTileM + cta_rank * kBlockM + r_in_tile;
+            uint32_t pk[kEpi == kMxEpiDgradDown ? 1 : 32];
+            if constexpr (kEpi == kMxEpiDgradDown) {
+                // d_hidden is an output of its own: each 32-column chunk goes from tensor memory straight to global
+                // memory as bf16 and is read back (this thread's own 64 bytes) when the SwiGLU backward needs it
+                __nv_bfloat16* dh16 = p.out_bf16 + row * p.ld_out + n_idx * kBlockN + sub * 64;
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t acc[32];
+                    tmem_ld_32x32(t_addr + (sub * 2 + c) * 32, acc);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int v = 0; v < 2; ++v)
+                        st_global_256(dh16 + c * 32 + v * 16,
+                                      pack_bf16(__uint_as_float(acc[16 * v + 0]), __uint_as_float(acc[16 * v + 1])),
+                                      pack_bf16(__uint_as_float(acc[16 * v + 2]), __uint_as_float(acc[16 * v + 3])),
+                                      pack_bf16(__uint_as_float(acc[16 * v + 4]), __uint_as_float(acc[16 * v + 5])),
+                                      pack_bf16(__uint_as_float(acc[16 * v + 6]), __uint_as_float(acc[16 * v + 7])),
+                                      pack_bf16(__uint_as_float(acc[16 * v + 8]), __uint_as_float(acc[16 * v + 9])),
+                                      pack_bf16(__uint_as_float(acc[16 * v + 10]), __uint_as_float(acc[16 * v + 11])),
+                                      pack_bf16(__uint_as_float(acc[16 * v + 12]), __uint_as_float(acc[16 * v + 13])),
+                                      pack_bf16(__uint_as_float(acc[16 * v + 14]), __uint_as_float(acc[16 * v + 15])));
+                }
+            } else {
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 // GateUp: chunk `sub` of the gate half and chunk `sub` of the up half; otherwise two adjacent chunks
@@ -367,11 +398,11 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
 #pragma unroll
                 for (int i = 0; i < 16; ++i) pk[c * 16 + i] = pack_bf16(__uint_as_float(acc[2 * i]), __uint_as_float(acc[2 * i + 1]));
             }
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) { if (k2) mbar_arrive_leader(tempty_bar); else mbar_arrive(tempty_bar); }   // accumulator is free
 
-            const size_t row = static_cast<size_t>(m_idx) * kTileM + cta_rank * kBlockM + r_in_tile;
             if constexpr (kEpi == kMxEpiStore) {
                 if (!(kWgrad && p.accumulate && k_tiles == 0)) {
                     __nv_bfloat16* dst = p.out_bf16 + (kWgrad ? static_cast<size_t>(expert) * p.out_expert_stride : 0) +
@@ -412,33 +443,37 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 mx_store_normal(h, p.q[2], p.sc[2], row, col0, p.q_cols);
                 mx_store_transposed(h, tr, p.qt[2], p.sct[2], row, col0, p.t_rows, lane);
             } else {
+                // d_hidden was stored above; it comes back 32 columns at a time (from L1/L2), so no copy of the
+                // accumulator stays in registers beside the SwiGLU temporaries
                 float inv_w = 0.0f;
                 if (p.row_scale) { const float w = p.row_scale[row]; inv_w = w > 0.0f ? 1.0f / w : 0.0f; }
                 float partial = 0.0f;
                 const int colbase = n_idx * kBlockN + sub * 64;
-                __nv_bfloat16* dh16 = p.out_bf16 + row * p.ld_out + colbase;
+                const __nv_bfloat16* dh16 = p.out_bf16 + row * p.ld_out + colbase;
                 const size_t so0 = mx_scale_offset(static_cast<int>(row), colbase >> 5, p.q_cols >> 7);   // 2 consecutive bytes
                 const uint32_t gsc2 = *reinterpret_cast<const uint16_t*>(p.in_sc[0] + so0);
                 const uint32_t usc2 = *reinterpret_cast<const uint16_t*>(p.in_sc[1] + so0);
-                uint32_t gv[2][8], uv[2][8];                 // 64 saved fp8 gate / up values each: two 256-bit loads
-#pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                    ld_global_256(p.in_q[0] + row * p.q_cols + colbase + v * 32, gv[v]);
-                    ld_global_256(p.in_q[1] + row * p.q_cols + colbase + v * 32, uv[v]);
-                }
-#pragma unroll
+#pragma unroll 1
                 for (int c = 0; c < 2; ++c) {
                     const int col0 = colbase + c * 32;
                     const float gs = mx_scale_value((gsc2 >> (8 * c)) & 0xFFu), us = mx_scale_value((usc2 >> (8 * c)) & 0xFFu);
-                    const uint32_t (&gb)[8] = gv[c];
-                    const uint32_t (&ub)[8] = uv[c];
+                    uint32_t gb[8], ub[8], dh[16];           // 32 saved fp8 gate / up values, 32 bf16 d_hidden values
+                    ld_global_256(p.in_q[0] + row * p.q_cols + col0, gb);
+                    ld_global_256(p.in_q[1] + row * p.q_cols + col0, ub);
+                    {
+                        uint32_t lo[8], hi[8];
+                        ld_global_256(dh16 + c * 32, lo);
+                        ld_global_256(dh16 + c * 32 + 16, hi);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) { dh[i] = lo[i]; dh[8 + i] = hi[i]; }
+                    }
                     uint32_t dg[16], du[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const uint16_t g2 = static_cast<uint16_t>(gb[i >> 1] >> ((i & 1) * 16));
                         const uint16_t u2 = static_cast<uint16_t>(ub[i >> 1] >> ((i & 1) * 16));
                         float2 gf = mx_unpack2(g2, gs), uf = mx_unpack2(u2, us);
-                        const float2 dhf = unpack_bf16(pk[c * 16 + i]);
+                        const float2 dhf = unpack_bf16(dh[i]);
                         bool gm0 = true, gm1 = true, um0 = true, um1 = true;
                         if (p.has_limit) {
                             gm0 = gf.x <= p.limit; gm1 = gf.y <= p.limit;
@@ -453,14 +488,9 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                         du[i] = pack_bf16(um0 ? silu0 * dhf.x : 0.0f, um1 ? silu1 * dhf.y : 0.0f);
                         partial += dhf.x * inv_w * (silu0 * uf.x) + dhf.y * inv_w * (silu1 * uf.y);
                     }
-#pragma unroll
-                    for (int v = 0; v < 2; ++v)
-                        st_global_256(dh16 + c * 32 + v * 16, pk[c * 16 + 8 * v], pk[c * 16 + 8 * v + 1], pk[c * 16 + 8 * v + 2],
-                                      pk[c * 16 + 8 * v + 3], pk[c * 16 + 8 * v + 4], pk[c * 16 + 8 * v + 5], pk[c * 16 + 8 * v + 6],
-                                      pk[c * 16 + 8 * v + 7]);
                     mx_store_normal(dg, p.q[0], p.sc[0], row, col0, p.q_cols);
-                    mx_store_normal(du, p.q[1], p.sc[1], row, col0, p.q_cols);
                     mx_store_transposed(dg, tr, p.qt[0], p.sct[0], row, col0, p.t_rows, lane);
+                    mx_store_normal(du, p.q[1], p.sc[1], row, col0, p.q_cols);
                     mx_store_transposed(du, tr, p.qt[1], p.sct[1], row, col0, p.t_rows, lane);
                 }
                 if (p.partials) p.partials[row * (4 * p.n_tiles) + 4 * n_idx + sub] = partial;   // four column slices per tile
