@@ -164,22 +164,41 @@ class ClockSampler:
 
 
 def bind_to_gpu_numa_node(local_rank: int):
-    """Runs this rank's host thread on the CPUs next to its GPU (read from NVML, nothing is set on the GPU), so that
-    the pinned buffers it allocates afterwards land in that node's memory and its copies do not cross the socket
-    link.  Returns the CPU count it bound to, or None when the affinity could not be read."""
+    """Best effort, host side only (nothing is set on the GPU): run this rank's host thread on the CPUs next to its GPU
+    and prefer that NUMA node for the memory it allocates from now on, so that the pinned buffers of the end-to-end
+    step and their copies do not cross the socket link.  The GPU's node comes from sysfs (its PCI device) and the
+    CPU list from NVML; a container whose CPU set excludes those CPUs keeps its affinity and only gets the memory
+    preference.  Returns a short description of what was done."""
+    done = {}
     try:
         import pynvml
         pynvml.nvmlInit()
         handle = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
-        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
-        cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1}
-        cpus &= os.sched_getaffinity(0)
-        if not cpus:
-            return None
-        os.sched_setaffinity(0, cpus)
-        return len(cpus)
-    except Exception:
-        return None
+        bus = pynvml.nvmlDeviceGetPciInfo(handle).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        if len(bus.split(":")[0]) == 8:                     # NVML prints an 8-digit domain, sysfs a 4-digit one
+            bus = bus[4:]
+        with open(f"/sys/bus/pci/devices/{bus}/numa_node") as fh:
+            node = int(fh.read().strip())
+        done["gpu_numa_node"] = node
+        try:
+            words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+            cpus = {64 * i + b for i, w in enumerate(words) for b in range(64) if (w >> b) & 1} & os.sched_getaffinity(0)
+            if cpus:
+                os.sched_setaffinity(0, cpus)
+                done["cpus_bound"] = len(cpus)
+        except Exception:
+            pass
+        if node >= 0:
+            import ctypes
+            libc = ctypes.CDLL(None, use_errno=True)
+            mask = ctypes.c_ulong(1 << node)
+            MPOL_PREFERRED, SYS_set_mempolicy = 1, 238     # x86-64
+            rc = libc.syscall(SYS_set_mempolicy, MPOL_PREFERRED, ctypes.byref(mask), ctypes.c_ulong(64))
+            done["memory_preferred_node"] = node if rc == 0 else f"refused (errno {ctypes.get_errno()})"
+    except Exception as e:                                  # no NVML, no sysfs entry, another architecture
+        done["skipped"] = type(e).__name__
+    return done
 
 
 def make_inputs(wl, rank, world, dev, pinned=True):
@@ -444,6 +463,27 @@ class LayerRun:
             torch.cuda.current_stream().wait_event(s["downloaded"][(i - 1) & 1])
             torch.cuda.current_stream().wait_event(s["uploaded"][i & 1])
 
+    def copy_only_step(self):
+        """The host<->device copies of one end-to-end step and nothing else (same pinned buffers, same two copy
+        streams, the downloads reading device tensors of the results' sizes): what the host side alone can sustain."""
+        s = self._e2e_state()
+        if "fake" not in s:
+            s["fake"] = (torch.empty_like(s["out_host"], device=self.dev), torch.empty_like(s["dx_host"], device=self.dev),
+                         torch.empty_like(s["drw_host"], device=self.dev))
+        with torch.cuda.stream(s["h2d"]):
+            for k in s["keys"]:
+                s["slots"][0][k].copy_(self.host[k], non_blocking=True)
+        with torch.cuda.stream(s["d2h"]):
+            s["out_host"].copy_(s["fake"][0], non_blocking=True)
+            if self.wl["backward"]:
+                s["dx_host"].copy_(s["fake"][1], non_blocking=True)
+                s["drw_host"].copy_(s["fake"][2], non_blocking=True)
+
+    def copy_only_finish(self):
+        s = self._e2e_state()
+        torch.cuda.current_stream().wait_stream(s["h2d"])
+        torch.cuda.current_stream().wait_stream(s["d2h"])
+
     def e2e_bytes(self):
         wl, s = self.wl, self._e2e_state()
         h2d = sum(v.numel() * v.element_size() for k, v in self.host.items() if k != "d_out" or wl["backward"])
@@ -524,6 +564,8 @@ class LayerRun:
             self.drain_e2e()
             res["ms_e2e"], _ = self.timed(self.step_e2e, steps, finish=self.drain_e2e)
             res["h2d"], res["d2h"] = self.e2e_bytes()
+            torch.cuda.synchronize()
+            res["ms_copy_only"], _ = self.timed(self.copy_only_step, min(steps, 20), finish=self.copy_only_finish)
         mok.raise_for_status(dev)
         return res
 
@@ -672,7 +714,7 @@ def run_ours(args, rank, world, local_rank):
               "l2": "inputs larger than L2 (no flush needed)", "per_gpu_tflops": per_gpu,
               "pct_of_measured_bf16_peak": 100.0 * per_gpu / sustained,
               "pct_of_measured_burst_peak": 100.0 * per_gpu / ((2.0 if wl.get("mxfp8") else 1.0) * peaks["burst"]),
-              "host_thread_bound_to_gpu_numa_cpus": numa_cpus}
+              "host_numa_placement": numa_cpus}
     if "parity" in res:
         config["parity_rel_l2"] = res["parity"]["worst_over_ranks"]
         config["parity"] = res["parity"]
@@ -709,7 +751,10 @@ def run_ours(args, rank, world, local_rank):
         "dtype": "mxfp8 (e4m3 x e8m0, fp32 accumulate)" if wl.get("mxfp8") else "bf16", "data": "synthetic",
         "config": config,
         "e2e": {"value": world * flops / (ms_e2e * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"]},
+                "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
+                "copies_alone_ms_per_step": res["ms_copy_only"],
+                "copies_alone_gb_per_s_per_gpu_each_way": (res["h2d"] + res["d2h"]) / 2 / (res["ms_copy_only"] * 1e-3) / 1e9,
+                "note": "copies_alone = the step's uploads and downloads with no compute, all ranks at once (max over ranks)"},
         "gpu_launches": res["launches"],
         "clocks": clocks,
         "roofline": roof,

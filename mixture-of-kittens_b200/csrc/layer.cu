@@ -398,10 +398,12 @@ extern "C" int mok_fwd_bf16(const mok_fwd_bf16_args* a, void* stream) {
     MOK_TRY(pipe.error());
     MOK_TRY(pipe.fork());
 
-    // shared expert on the local tokens (overlaps the first dispatch chunk)
+    // shared expert on the local tokens: its gate|up GEMM runs beside the first dispatch; its down projection beside
+    // the first dispatch too when the window is moved in one piece, beside the last combine chunk when it is chunked
     MOK_TRY(run_gate_up(c, whole, d, false, 0, d.T, x_local, d.T, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
                         a->hidden_shared, s));
-    MOK_TRY(run_down(c, whole, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
+    const bool shared_down_last = chunks > 1;
+    if (!shared_down_last) MOK_TRY(run_down(c, whole, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
 
     const int n_macro = (d.cap + d.MB - 1) / d.MB;
     for (int m = n_macro - 1; m >= 0; --m) {
@@ -425,6 +427,8 @@ extern "C" int mok_fwd_bf16(const mok_fwd_bf16_args* a, void* stream) {
                 comb.peers = combine_peers;
                 return launch_combine_rows(comb, move_grid(x), st);
             }));
+        if (m == 0 && shared_down_last)
+            MOK_TRY(run_down(c, whole, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
         MOK_TRY(pipe.join());      // the next window reuses the buffers
         if (m > 0) MOK_TRY(pipe.fork());
     }
@@ -500,11 +504,14 @@ extern "C" int mok_bwd_bf16(const mok_bwd_bf16_args* a, void* stream) {
                 rd.partial_cols = partial_cols;
                 return launch_combine_rows(rd, move_grid(x), st);
             }));
-        MOK_TRY(pipe.join());
+        // the weight gradients read what the loads and the GEMMs of this window produced, all ordered before this
+        // point of the caller's stream; the last reverse-dispatch chunk, still running on the side stream, reads
+        // d_x_routed and the partials, which they do not touch: they overlap, and the join comes after them
         const int acc = m > 0 ? 1 : 0;
         MOK_TRY(run_wgrad(c, whole, true, off, limit, a->d_y_routed, d.H, a->hidden_routed, d.I, d.MB, a->d_w_routed_down, acc, s));
         MOK_TRY(run_wgrad(c, whole, true, off, limit, a->d_gate_routed, d.I, a->x_routed, d.H, d.MB, a->d_w_routed_gate, acc, s));
         MOK_TRY(run_wgrad(c, whole, true, off, limit, a->d_up_routed, d.I, a->x_routed, d.H, d.MB, a->d_w_routed_up, acc, s));
+        MOK_TRY(pipe.join());      // the next window replays into the buffers the stores read
     }
     return MOK_OK;
 }
@@ -670,7 +677,8 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
 
     MOK_TRY(run_gate_up(c, whole, d, false, 0, d.T, x_local, d.T, a->w_shared_gate, a->w_shared_up, a->gate_shared, a->up_shared,
                         a->hidden_shared, s));
-    MOK_TRY(run_down(c, whole, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
+    const bool shared_down_last = chunks > 1;      // as in mok_fwd_bf16
+    if (!shared_down_last) MOK_TRY(run_down(c, whole, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
 
     const int n_macro = (d.cap + d.MB - 1) / d.MB;
     for (int m = n_macro - 1; m >= 0; --m) {
@@ -697,6 +705,8 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
                 comb.peers = combine_peers;
                 return launch_combine_rows(comb, move_grid(x), st);
             }));
+        if (m == 0 && shared_down_last)
+            MOK_TRY(run_down(c, whole, d, false, 0, d.T, a->hidden_shared, d.T, a->w_shared_down, a->y_shared, s));
         MOK_TRY(pipe.join());
         if (m > 0) MOK_TRY(pipe.fork());
     }
@@ -809,14 +819,14 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                 rd.partial_cols = 4 * partial_cols   /* the MXFP8 epilogue writes one partial per 64-column slice */;
                 return launch_combine_rows(rd, move_grid(x), st);
             }));
-        MOK_TRY(pipe.join());
-        const int acc = m > 0 ? 1 : 0;
+        const int acc = m > 0 ? 1 : 0;      // weight gradients beside the last reverse-dispatch chunk, as in mok_bwd_bf16
         MOK_TRY(mx_wgrad(c, whole, d, off, limit, a->work_d_y_qt, a->work_d_y_sct, d.H, a->hidden_qt, a->hidden_sct, d.I,
                          a->d_w_routed_down, acc, s));
         MOK_TRY(mx_wgrad(c, whole, d, off, limit, a->work_d_gate_qt, a->work_d_gate_sct, d.I, a->x_qt, a->x_sct, d.H,
                          a->d_w_routed_gate, acc, s));
         MOK_TRY(mx_wgrad(c, whole, d, off, limit, a->work_d_up_qt, a->work_d_up_sct, d.I, a->x_qt, a->x_sct, d.H,
                          a->d_w_routed_up, acc, s));
+        MOK_TRY(pipe.join());
     }
     return MOK_OK;
 }

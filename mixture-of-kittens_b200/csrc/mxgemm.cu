@@ -14,6 +14,14 @@ int launch_mx_inst(const CUtensorMap& a0, const CUtensorMap& b0, const CUtensorM
     int dev = 0;
     MOK_CUDA_CHECK(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64 || !configured[dev]) {
+        // setmaxnreg only redistributes the registers the CTA was launched with: refuse to launch a build whose
+        // allocation cannot cover the two role budgets (the growing warps would wait for registers that never come)
+        cudaFuncAttributes fa{};
+        MOK_CUDA_CHECK(cudaFuncGetAttributes(&fa, kern));
+        if (kMxThreads * fa.numRegs < 128 * mx_light_regs(kEpi, k2) + (kMxThreads - 128) * mx_epi_regs(kEpi, k2)) {
+            note_error_text("mx_gemm_kernel: register allocation of this build is smaller than its setmaxnreg budgets");
+            return MOK_ERR_UNSUPPORTED;
+        }
         MOK_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         if (dev >= 0 && dev < 64) configured[dev] = true;
     }

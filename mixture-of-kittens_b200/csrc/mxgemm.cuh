@@ -50,9 +50,15 @@ constexpr int kMxEpiGroups = 4;                       // epilogue warps per TMEM
 constexpr int kMxEpiWarps = 4 * kMxEpiGroups;
 constexpr int kMxThreads = 128 + 32 * kMxEpiWarps;    // warps 0-3: producer, MMA issuer, two spare; warps 4-19: epilogue
 // Registers are re-balanced between the roles with setmaxnreg (it works on groups of four warps, hence the two spare
-// warps): the kernel starts with 96 registers per thread (five warps share each of the SM's four register files), the
-// first group gives up half of its share and the sixteen epilogue warps grow to 112.
-constexpr int kMxLightRegs = 48, kMxEpiRegs = 112;
+// warps).  A CTA can only redistribute what it was given: 640 threads x 96 registers (five warps share each of the SM's
+// four register files, which caps a thread at 96 at launch).  The first group gives up a third of its share and the
+// sixteen epilogue warps grow to 104; the fused epilogues of the one-CTA form (leaner producer and issuer loops) run with
+// 32 and 112 instead.  The launcher checks the sum against the kernel's actual allocation.
+constexpr int kMxLaunchRegs = 96;
+__host__ __device__ constexpr int mx_light_regs(int epi, bool k2) { return (k2 || epi == 0) ? 64 : 32; }
+__host__ __device__ constexpr int mx_epi_regs(int epi, bool k2) { return (k2 || epi == 0) ? 104 : 112; }
+static_assert(128 * mx_light_regs(0, true) + 512 * mx_epi_regs(0, true) <= 640 * kMxLaunchRegs, "register budget");
+static_assert(128 * mx_light_regs(1, false) + 512 * mx_epi_regs(1, false) <= 640 * kMxLaunchRegs, "register budget");
 constexpr int kMxTrBytes = kMxEpiWarps * 32 * 17 * 4; // per-epilogue-warp transpose tiles
 __host__ __device__ constexpr int mx_smem_bytes(int epi, bool k2) {
     return mx_stages(epi, k2) * (mx_tile_bytes(k2) + kMxSfBytes) + 256 + kMaxExperts * 4 + (epi == 0 ? 0 : kMxTrBytes) + 1024;
@@ -231,7 +237,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
     };
 
     if (warp < 4) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kMxLightRegs));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(mx_light_regs(kEpi, k2)));
     if (warp == 0) {
         // ------------------------------------------------------------------ producer
         if (lane == 0) {
@@ -344,7 +350,7 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         }
     }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kMxEpiRegs));
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(mx_epi_regs(kEpi, k2)));
         // ------------------------------------------------------------------ epilogue warps
         // Sixteen warps: four per TMEM lane quarter (a warp may only read lanes 32*(warp%4)...), each taking
         // 64 of the tile's 256 columns, so a thread holds its share of the accumulator as 32 packed words.
@@ -426,20 +432,24 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 }
             } else if constexpr (kEpi == kMxEpiGateUp) {
                 const int col0 = n_idx * (kBlockN / 2) + sub * 32;
-                uint32_t g[16], u[16], h[16];
+                // saved gate and up go out first; the hidden chunk is formed only after their temporaries are dead
+                {
+                    uint32_t g[16], u[16];
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) { g[i] = pk[i]; u[i] = pk[16 + i]; }
+                    mx_store_normal(g, p.q[0], p.sc[0], row, col0, p.q_cols);
+                    mx_store_normal(u, p.q[1], p.sc[1], row, col0, p.q_cols);
+                }
+                uint32_t h[16];
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    g[i] = pk[i];
-                    u[i] = pk[16 + i];
-                    float2 gf = unpack_bf16(g[i]), uf = unpack_bf16(u[i]);
+                    float2 gf = unpack_bf16(pk[i]), uf = unpack_bf16(pk[16 + i]);
                     if (p.has_limit) {
                         gf.x = fminf(gf.x, p.limit); gf.y = fminf(gf.y, p.limit);
                         uf.x = fminf(fmaxf(uf.x, -p.limit), p.limit); uf.y = fminf(fmaxf(uf.y, -p.limit), p.limit);
                     }
                     h[i] = pack_bf16(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
                 }
-                mx_store_normal(g, p.q[0], p.sc[0], row, col0, p.q_cols);
-                mx_store_normal(u, p.q[1], p.sc[1], row, col0, p.q_cols);
                 mx_store_normal(h, p.q[2], p.sc[2], row, col0, p.q_cols);
                 mx_store_transposed(h, tr, p.qt[2], p.sct[2], row, col0, p.t_rows, lane);
             } else {
@@ -457,23 +467,18 @@ mx_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
                 for (int c = 0; c < 2; ++c) {
                     const int col0 = colbase + c * 32;
                     const float gs = mx_scale_value((gsc2 >> (8 * c)) & 0xFFu), us = mx_scale_value((usc2 >> (8 * c)) & 0xFFu);
-                    uint32_t gb[8], ub[8], dh[16];           // 32 saved fp8 gate / up values, 32 bf16 d_hidden values
+                    uint32_t gb[8], ub[8], dh[2][8];         // 32 saved fp8 gate / up values, 32 bf16 d_hidden values
                     ld_global_256(p.in_q[0] + row * p.q_cols + col0, gb);
                     ld_global_256(p.in_q[1] + row * p.q_cols + col0, ub);
-                    {
-                        uint32_t lo[8], hi[8];
-                        ld_global_256(dh16 + c * 32, lo);
-                        ld_global_256(dh16 + c * 32 + 16, hi);
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) { dh[i] = lo[i]; dh[8 + i] = hi[i]; }
-                    }
+                    ld_global_256(dh16 + c * 32, dh[0]);
+                    ld_global_256(dh16 + c * 32 + 16, dh[1]);
                     uint32_t dg[16], du[16];
 #pragma unroll
                     for (int i = 0; i < 16; ++i) {
                         const uint16_t g2 = static_cast<uint16_t>(gb[i >> 1] >> ((i & 1) * 16));
                         const uint16_t u2 = static_cast<uint16_t>(ub[i >> 1] >> ((i & 1) * 16));
                         float2 gf = mx_unpack2(g2, gs), uf = mx_unpack2(u2, us);
-                        const float2 dhf = unpack_bf16(dh[i]);
+                        const float2 dhf = unpack_bf16(dh[i >> 3][i & 7]);
                         bool gm0 = true, gm1 = true, um0 = true, um1 = true;
                         if (p.has_limit) {
                             gm0 = gf.x <= p.limit; gm1 = gf.y <= p.limit;
