@@ -373,6 +373,13 @@ class LayerRun:
         self.ws = F.get_workspace(self.cfg, group, device=self.dev, num_local_tokens=T, hidden_size=H, topk=K)
         self.host, params = make_inputs(wl, rank, world, self.dev)
         self.dev_in = {k: v.to(self.dev) for k, v in self.host.items()}
+        if world > 1:
+            # the device-resident step finds its inputs where a producer running on this GPU would have written
+            # them: in the workspace's rank-visible buffers, which mok.functional then uses in place (no staging copy)
+            self.dev_in["x"] = self.ws.x_buffer.copy_(self.dev_in["x"])
+            self.dev_in["rw"] = self.ws.router_weight_buffer.copy_(self.dev_in["rw"])
+            if wl["backward"]:
+                self.dev_in["d_out"] = self.ws.d_y_buffer.copy_(self.dev_in["d_out"])
         # share of all routes that lands on the busiest rank (1/world when balanced)
         dest = torch.bincount((self.dev_in["topk"] // self.El).flatten(), minlength=world).double()
         if world > 1:
@@ -682,6 +689,7 @@ def run_ours(args, rank, world, local_rank):
         assert torch.equal(graph_out[0], eager_out[0]), "graph replay differs from the eager step"
         ms_graph, _ = run.timed(graph.replay, steps)
     clocks = sampler.stop() if rank == 0 else None
+    comm_sms_used = (run.cfg.fwd_num_comm_sms, run.cfg.bwd_num_comm_sms)
     sweep = None
     if args.sweep_comm_sms and world > 1:      # the same workload with other numbers of SMs set aside for row movement
         sweep = []
@@ -703,7 +711,9 @@ def run_ours(args, rank, world, local_rank):
     config = {"workload": f"{name}: {wl['desc']}", "ep_size": world, "tokens_per_rank": T, "hidden": H,
               "intermediate": I, "experts": E, "topk": K, "minibatch_size": wl["minibatch"],
               "macrobatch_size": wl["macrobatch"], "capacity_multiplier": wl["multiplier"],
-              "fwd_num_comm_sms": run.cfg.fwd_num_comm_sms, "bwd_num_comm_sms": run.cfg.bwd_num_comm_sms,
+              "fwd_num_comm_sms": comm_sms_used[0], "bwd_num_comm_sms": comm_sms_used[1],
+              "comm_sms_form": "dedicated SMs" if os.environ.get("MOK_B200_DEDICATED_COMM_SMS", "0") not in ("", "0")
+              else "4 thin mover CTAs per budgeted SM beside the GEMM CTAs",
               "busiest_rank_share_of_routes": run.max_rank_share,
               "pass": "fwd+bwd" if wl["backward"] else "fwd (incl. build_schedule)",
               "rank0_schedule_rows": res["n_rows"], "rank0_routes": res["n_routes"],

@@ -182,14 +182,14 @@ typedef struct mok_layer_common {
     int ep_size, ep_rank;
     int num_local_tokens, hidden, intermediate, num_local_experts, topk;
     int schedule_capacity, macrobatch_size, minibatch_size;
-    int num_comm_sms;                       /* SMs set aside for row movement while the GEMMs run, as the reference's
-                                               fwd/bwd_num_comm_sms (mok/functional.py:22-29): with ep_size > 1 and a
-                                               window cut into chunks (at least two minibatches), dispatch and combine
-                                               run as this many bulk-copy CTAs on SMs of their own and the routed GEMM
-                                               grids shrink by the same number (capped at half the GPU).  With one rank
-                                               the movers are thin CTAs beside the GEMMs and the value is not used.
-                                               MOK_B200_COMM_SMS in the environment overrides it (0 = thin CTAs that
-                                               share SMs with the GEMMs at any ep_size). */
+    int num_comm_sms;                       /* SM budget of the row movement, as the reference's fwd/bwd_num_comm_sms
+                                               (mok/functional.py:22-29).  Used with ep_size > 1 while a window is cut into
+                                               chunks (at least two minibatches): dispatch and combine run as 4 thin
+                                               bulk-copy CTAs per budgeted SM beside the GEMM CTAs (default), or, with
+                                               MOK_B200_DEDICATED_COMM_SMS=1, as one fat CTA on each of that many SMs of
+                                               their own while the routed GEMM grids shrink by the same number (capped at
+                                               half the GPU).  Results never depend on it.  MOK_B200_COMM_SMS in the
+                                               environment overrides the value of every call. */
     int has_swiglu_limit;
     float swiglu_limit;
     int defer_combine;                      /* 1: leave the routed results in their rows (y_routed, or d_x_routed and the

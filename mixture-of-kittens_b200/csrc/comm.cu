@@ -194,8 +194,10 @@ __device__ __forceinline__ void bulk_s2g(void* gmem_dst, const void* smem_src, u
     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }
 
+// (compiled for at most 32 registers per thread: beside a 640-thread MXFP8 GEMM CTA each of the SM's four register
+// files has room for exactly one such warp)
 template <int kMode>
-__global__ void __launch_bounds__(kMoveMaxWarps * 32) move_rows_kernel(RowMoveParams p) {
+__global__ void __launch_bounds__(kMoveMaxWarps * 32, 8) move_rows_kernel(RowMoveParams p) {
     extern __shared__ __align__(128) uint8_t slot_mem[];      // [warps][2][piece]
     __shared__ __align__(8) uint64_t bars[kMoveMaxWarps][2];
     const int kMoveWarps = static_cast<int>(blockDim.x >> 5);
@@ -412,12 +414,13 @@ int launch_dispatch_quant(const RowMoveParams& p, const QuantOut& out, bool scal
     return MOK_OK;
 }
 
-// Two shapes of mover CTA: "thin" (3 warps x 2 x 4 KB = 24 KB, many CTAs, fits beside a GEMM CTA) and
-// "fat" (8 warps x 2 x 8 KB = 128 KB, a few CTAs that each take an SM of their own).
+// Three shapes of mover CTA: "thin" (3 warps x 2 x 4 KB = 24 KB, many CTAs, fits beside a BF16 GEMM CTA), "lean"
+// (2 warps, 16 KB: what the MXFP8 GEMM CTAs leave free) and "fat" (8 warps x 2 x 8 KB = 128 KB, a few CTAs that
+// each take an SM of their own).
 template <int kMode>
 int launch_move(RowMoveParams p, int num_blocks, cudaStream_t stream) {
     const bool fat = p.fat_ctas != 0;
-    const int warps = fat ? 8 : 3;
+    const int warps = fat ? 8 : (p.lean ? 2 : 3);
     p.piece_bytes = fat ? 8192 : 4096;
     const int smem = warps * 2 * p.piece_bytes;
     static bool configured[64] = {false};

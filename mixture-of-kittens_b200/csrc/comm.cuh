@@ -27,6 +27,7 @@ struct RowMoveParams {
     int partial_cols;
     int* status;               // device status word (bounded waits report here)
     int fat_ctas;              // 1: few CTAs with 128 KB of copy slots each (dedicated SMs); 0: many thin CTAs
+    int lean;                  // thin CTAs of two warps and 16 KB (what fits beside an MXFP8 GEMM CTA) instead of three and 24 KB
     int piece_bytes;           // set by the launcher
 };
 

@@ -54,7 +54,8 @@ int fill_peers(PeerPtrs& out, const uint64_t* ptrs, int W) {
 struct PassCtx {
     ChunkSpec chunk = {0, 1, 0};   // row sub-range of the window the launch covers
     int gemm_ctas = 0;             // cap on the CTAs of routed GEMM launches (0 = all SMs)
-    int comm_sms = 0;              // > 0: the row movers run as this many fat CTAs on SMs of their own
+    int comm_sms = 0;              // > 0: the call's communication-SM budget applies to the row movers of this launch
+    bool dedicated = false;        // the budget is SMs of the movers' own (fat CTAs), not mover CTAs beside the GEMM CTAs
 };
 
 GemmParams base_params(const mok_layer_common& c, const PassCtx& x, bool routed, int off, int limit) {
@@ -190,7 +191,7 @@ RowMoveParams row_move(const mok_layer_common& c, const PassCtx& x, const Dims& 
     r.hidden = d.H;
     r.row_divisor = 1;
     r.status = c.status;
-    r.fat_ctas = x.comm_sms > 0 ? 1 : 0;
+    r.fat_ctas = (x.comm_sms > 0 && x.dedicated) ? 1 : 0;
     r.chunk = x.chunk;
     return r;
 }
@@ -206,12 +207,15 @@ RowMoveParams row_move(const mok_layer_common& c, const PassCtx& x, const Dims& 
 //     main:          compute(0)              compute(1)              ...
 // Dependencies are CUDA events only (no kernel waits on another kernel), the side stream forks from
 // and joins back into the caller's stream inside the call, and results do not depend on timing.
-// Two shapes of mover launch: by default thin CTAs that share SMs with the persistent GEMM CTAs; with
-// `comm_sms` > 0 (the reference's fwd/bwd_num_comm_sms) that many fat CTAs on SMs of their own, the
-// routed GEMM grids shrinking by the same number.
-// Even an unchunked window puts its load on the side stream, so that it runs beside whatever the caller's
-// stream holds since the last fork (the dense shared expert: tensor-bound, while the row gather is
-// memory-bound).
+// `comm_sms` (the reference's fwd/bwd_num_comm_sms) is the SM budget of the row movement while a chunked window runs.
+// Shared form (default): the movers are thin bulk-copy CTAs, four per budgeted SM, that sit beside the persistent
+// GEMM CTAs (24 KB of shared memory and three warps fit next to one), so the GEMMs keep every SM and the budget sets
+// how many copy pipelines are in flight.  Dedicated form (MOK_B200_DEDICATED_COMM_SMS=1): that many SMs run fat mover
+// CTAs of their own and the routed GEMM grids shrink by the same number, as in the reference's megakernel.  Measured
+// on two B200s the shared form is 6 % faster, which is why it is the default.
+// With MOK_B200_OVERLAP_SHARED=1 even an unchunked window puts its load on the side stream, so that it runs beside
+// whatever the caller's stream holds since the last fork (the dense shared expert).  Off by default: measured on one
+// B200 the two kernels slow each other down by what the overlap saves (step within 1 % either way).
 // -------------------------------------------------------------------------------------------------
 namespace mok {
 namespace {
@@ -230,14 +234,18 @@ int env_int(const char* name, int fallback) {
     return e ? std::atoi(e) : fallback;
 }
 
-// MOK_B200_COMM_SMS: -1 / unset = take the count from the call's num_comm_sms; 0 = thin movers that share
-// SMs with the GEMMs whatever the call says; n > 0 = n SMs whatever the call says
+// MOK_B200_COMM_SMS: -1 / unset = take the budget from the call's num_comm_sms; 0 = no budget (four thin mover CTAs
+// per SM of the GPU whatever the call says); n > 0 = n SMs whatever the call says
 int comm_sm_override() {
     static const int configured = [] { const int v = env_int("MOK_B200_COMM_SMS", -1); return v > 64 ? 64 : v; }();
     return configured;
 }
+bool dedicated_comm_sms() {
+    static const bool on = env_int("MOK_B200_DEDICATED_COMM_SMS", 0) != 0;
+    return on;
+}
 bool overlap_shared_expert() {
-    static const bool on = env_int("MOK_B200_OVERLAP_SHARED", 1) != 0;
+    static const bool on = env_int("MOK_B200_OVERLAP_SHARED", 0) != 0;
     return on;
 }
 
@@ -317,7 +325,11 @@ private:
     PassCtx ctx(int c) const {
         PassCtx x;
         x.chunk = ChunkSpec{c, chunks_, min_rows_};
-        if (comm_sms_ > 0) { x.comm_sms = comm_sms_; x.gemm_ctas = device_sm_count() - comm_sms_; }
+        if (comm_sms_ > 0) {
+            x.comm_sms = comm_sms_;
+            x.dedicated = dedicated_comm_sms();
+            if (x.dedicated) x.gemm_ctas = device_sm_count() - comm_sms_;
+        }
         return x;
     }
     int record(cudaStream_t s, cudaEvent_t& out) {
@@ -345,17 +357,21 @@ private:
     int rc_ = MOK_OK;
 };
 
-// CTAs of a row-movement launch: the dedicated SMs' worth of fat CTAs, or thin CTAs that share the SMs with
-// the persistent GEMM CTAs (four per SM; MOK_B200_COMM_BLOCKS overrides)
+// CTAs of a row-movement launch: four thin CTAs per budgeted SM beside the GEMM CTAs, or one fat CTA per dedicated
+// SM; without a budget (one rank, or a window moved in one piece) four thin CTAs per SM of the GPU
+// (MOK_B200_COMM_BLOCKS overrides that default)
 int move_grid(const PassCtx& x) {
-    if (x.comm_sms > 0) return x.comm_sms;
+    if (x.comm_sms > 0) return x.dedicated ? x.comm_sms : 4 * x.comm_sms;
     static const int configured = env_int("MOK_B200_COMM_BLOCKS", 0);
     return configured > 0 ? configured : device_sm_count() * 4;
 }
 
 // the quantising dispatch is arithmetic-heavy and its CTAs are small (33 KB of shared memory, 256 threads): six of
-// them fill a dedicated SM, and they do not fit beside an MXFP8 GEMM CTA, so they stay on the SMs set aside
-int quant_grid(const PassCtx& x) { return x.comm_sms > 0 ? x.comm_sms * 6 : move_grid(x); }
+// them fill a dedicated SM; in the shared form they take whatever SMs the GEMM launches leave free
+int quant_grid(const PassCtx& x) {
+    if (x.comm_sms > 0) return x.dedicated ? x.comm_sms * 6 : std::max(4 * x.comm_sms, 2 * device_sm_count());
+    return move_grid(x);
+}
 
 int pipeline_chunks(const mok_layer_common& c, int limit) {
     static const int configured = [] { const int v = env_int("MOK_B200_CHUNKS", 0); return v < 0 ? 0 : (v > 32 ? 32 : v); }();
@@ -703,6 +719,7 @@ extern "C" int mok_fwd_mxfp8(const mok_fwd_mxfp8_args* a, void* stream) {
                 if (c.defer_combine) return static_cast<int>(MOK_OK);   // mok_fwd_epilogue_rows reads y_routed in place
                 RowMoveParams comb = row_move(c, x, d, off, limit, a->y_routed);
                 comb.peers = combine_peers;
+                comb.lean = 1;
                 return launch_combine_rows(comb, move_grid(x), st);
             }));
         if (m == 0 && shared_down_last)
@@ -817,6 +834,7 @@ extern "C" int mok_bwd_mxfp8(const mok_bwd_mxfp8_args* a, void* stream) {
                 rd.scale_peers = drw_peers;
                 rd.partials = a->d_router_weight_partials;
                 rd.partial_cols = 4 * partial_cols   /* the MXFP8 epilogue writes one partial per 64-column slice */;
+                rd.lean = 1;
                 return launch_combine_rows(rd, move_grid(x), st);
             }));
         const int acc = m > 0 ? 1 : 0;      // weight gradients beside the last reverse-dispatch chunk, as in mok_bwd_bf16
