@@ -427,7 +427,8 @@ class LayerRun:
                 downloaded=[torch.cuda.Event() for _ in range(2)], i=0, primed=False,
                 out_host=torch.empty(T, H, dtype=torch.bfloat16).pin_memory(),
                 dx_host=torch.empty(T, H, dtype=torch.bfloat16).pin_memory(),
-                drw_host=torch.empty(T, K, dtype=torch.float32).pin_memory())
+                drw_host=torch.empty(T, K, dtype=torch.float32).pin_memory(),
+                metric_host=torch.empty(3, dtype=torch.float32).pin_memory())
         return self._e2e
 
     def _upload(self, s, slot):
@@ -437,7 +438,13 @@ class LayerRun:
                 s["slots"][slot][k].copy_(self.host[k], non_blocking=True)
             s["uploaded"][slot].record(s["h2d"])
 
-    def step_e2e(self):
+    def step_e2e_metric(self):
+        """The end-to-end step with a scalar result: the same uploads, but what goes back to the host is one number
+        per result tensor (its mean square, reduced on the device inside the timed region), as a trainer would read a
+        loss, instead of the tensors themselves."""
+        return self.step_e2e(metric_only=True)
+
+    def step_e2e(self, metric_only=False):
         s = self._e2e_state()
         i = s["i"]
         slot = i & 1
@@ -449,15 +456,25 @@ class LayerRun:
         self._upload(s, slot ^ 1)                          # prefetch the next step's inputs
         main.wait_event(s["uploaded"][slot])
         out, grads = self.step(s["slots"][slot])
+        metric = None
+        if metric_only:
+            parts = [out.float().square().mean()]
+            if grads is not None:
+                parts += [grads[0].float().square().mean(), grads[1].square().mean()]
+            metric = torch.stack(parts)
         s["consumed"][slot].record(main)
         with torch.cuda.stream(s["d2h"]):
             s["d2h"].wait_event(s["consumed"][slot])
-            s["out_host"].copy_(out, non_blocking=True)
-            out.record_stream(s["d2h"])
-            if grads is not None:
-                s["dx_host"].copy_(grads[0], non_blocking=True)
-                s["drw_host"].copy_(grads[1], non_blocking=True)
-                grads[0].record_stream(s["d2h"]); grads[1].record_stream(s["d2h"])
+            if metric is not None:
+                s["metric_host"][:metric.numel()].copy_(metric, non_blocking=True)
+                metric.record_stream(s["d2h"])
+            else:
+                s["out_host"].copy_(out, non_blocking=True)
+                out.record_stream(s["d2h"])
+                if grads is not None:
+                    s["dx_host"].copy_(grads[0], non_blocking=True)
+                    s["drw_host"].copy_(grads[1], non_blocking=True)
+                    grads[0].record_stream(s["d2h"]); grads[1].record_stream(s["d2h"])
             s["downloaded"][slot].record(s["d2h"])
         if i > 0:
             s["downloaded"][slot ^ 1].synchronize()        # the caller reads the previous step's results
@@ -573,6 +590,10 @@ class LayerRun:
             res["h2d"], res["d2h"] = self.e2e_bytes()
             torch.cuda.synchronize()
             res["ms_copy_only"], _ = self.timed(self.copy_only_step, min(steps, 20), finish=self.copy_only_finish)
+            for _ in range(2):
+                self.step_e2e_metric()
+            self.drain_e2e()
+            res["ms_e2e_metric"], _ = self.timed(self.step_e2e_metric, min(steps, 50), finish=self.drain_e2e)
         mok.raise_for_status(dev)
         return res
 
@@ -713,7 +734,7 @@ def run_ours(args, rank, world, local_rank):
               "macrobatch_size": wl["macrobatch"], "capacity_multiplier": wl["multiplier"],
               "fwd_num_comm_sms": comm_sms_used[0], "bwd_num_comm_sms": comm_sms_used[1],
               "comm_sms_form": "dedicated SMs" if os.environ.get("MOK_B200_DEDICATED_COMM_SMS", "0") not in ("", "0")
-              else "4 thin mover CTAs per budgeted SM beside the GEMM CTAs",
+              else "16 thin mover CTAs per budgeted SM beside the GEMM CTAs",
               "busiest_rank_share_of_routes": run.max_rank_share,
               "pass": "fwd+bwd" if wl["backward"] else "fwd (incl. build_schedule)",
               "rank0_schedule_rows": res["n_rows"], "rank0_routes": res["n_routes"],
@@ -764,7 +785,12 @@ def run_ours(args, rank, world, local_rank):
                 "h2d_bytes_per_step": res["h2d"], "d2h_bytes_per_step": res["d2h"],
                 "copies_alone_ms_per_step": res["ms_copy_only"],
                 "copies_alone_gb_per_s_per_gpu_each_way": (res["h2d"] + res["d2h"]) / 2 / (res["ms_copy_only"] * 1e-3) / 1e9,
-                "note": "copies_alone = the step's uploads and downloads with no compute, all ranks at once (max over ranks)"},
+                "note": "copies_alone = the step's uploads and downloads with no compute, all ranks at once (max over ranks)",
+                "scalar_result": {"value": world * flops / (res["ms_e2e_metric"] * 1e-3) / 1e12, "unit": UNIT,
+                                  "ms_per_step": res["ms_e2e_metric"], "h2d_bytes_per_step": res["h2d"],
+                                  "d2h_bytes_per_step": 12 if wl["backward"] else 4,
+                                  "note": "same uploads; the host reads one mean-square per result tensor (reduced on the "
+                                          "device inside the timed region) instead of the tensors"}},
         "gpu_launches": res["launches"],
         "clocks": clocks,
         "roofline": roof,

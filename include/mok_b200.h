@@ -184,7 +184,7 @@ typedef struct mok_layer_common {
     int schedule_capacity, macrobatch_size, minibatch_size;
     int num_comm_sms;                       /* SM budget of the row movement, as the reference's fwd/bwd_num_comm_sms
                                                (mok/functional.py:22-29).  Used with ep_size > 1 while a window is cut into
-                                               chunks (at least two minibatches): dispatch and combine run as 4 thin
+                                               chunks (at least two minibatches): dispatch and combine run as 16 thin
                                                bulk-copy CTAs per budgeted SM beside the GEMM CTAs (default), or, with
                                                MOK_B200_DEDICATED_COMM_SMS=1, as one fat CTA on each of that many SMs of
                                                their own while the routed GEMM grids shrink by the same number (capped at

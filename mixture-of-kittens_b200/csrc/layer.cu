@@ -208,9 +208,10 @@ RowMoveParams row_move(const mok_layer_common& c, const PassCtx& x, const Dims& 
 // Dependencies are CUDA events only (no kernel waits on another kernel), the side stream forks from
 // and joins back into the caller's stream inside the call, and results do not depend on timing.
 // `comm_sms` (the reference's fwd/bwd_num_comm_sms) is the SM budget of the row movement while a chunked window runs.
-// Shared form (default): the movers are thin bulk-copy CTAs, four per budgeted SM, that sit beside the persistent
-// GEMM CTAs (24 KB of shared memory and three warps fit next to one), so the GEMMs keep every SM and the budget sets
-// how many copy pipelines are in flight.  Dedicated form (MOK_B200_DEDICATED_COMM_SMS=1): that many SMs run fat mover
+// Shared form (default): the movers are thin bulk-copy CTAs, sixteen per budgeted SM, that sit beside the persistent
+// GEMM CTAs (24 KB of shared memory and three warps fit next to one) and fill an SM whenever no GEMM CTA holds it, so
+// the GEMMs keep every SM and the budget sets how many copy pipelines exist (the reference's defaults, 40 and 28 SMs,
+// give 640 and 448 mover CTAs; measured on two B200s the step gets shorter up to about 600 and flat beyond).  Dedicated form (MOK_B200_DEDICATED_COMM_SMS=1): that many SMs run fat mover
 // CTAs of their own and the routed GEMM grids shrink by the same number, as in the reference's megakernel.  Measured
 // on two B200s the shared form is 6 % faster, which is why it is the default.
 // With MOK_B200_OVERLAP_SHARED=1 even an unchunked window puts its load on the side stream, so that it runs beside
@@ -357,11 +358,12 @@ private:
     int rc_ = MOK_OK;
 };
 
-// CTAs of a row-movement launch: four thin CTAs per budgeted SM beside the GEMM CTAs, or one fat CTA per dedicated
+// CTAs of a row-movement launch: sixteen thin CTAs per budgeted SM beside the GEMM CTAs, or one fat CTA per dedicated
 // SM; without a budget (one rank, or a window moved in one piece) four thin CTAs per SM of the GPU
 // (MOK_B200_COMM_BLOCKS overrides that default)
+constexpr int kThinCtasPerBudgetedSm = 16;
 int move_grid(const PassCtx& x) {
-    if (x.comm_sms > 0) return x.dedicated ? x.comm_sms : 4 * x.comm_sms;
+    if (x.comm_sms > 0) return x.dedicated ? x.comm_sms : kThinCtasPerBudgetedSm * x.comm_sms;
     static const int configured = env_int("MOK_B200_COMM_BLOCKS", 0);
     return configured > 0 ? configured : device_sm_count() * 4;
 }
@@ -369,7 +371,7 @@ int move_grid(const PassCtx& x) {
 // the quantising dispatch is arithmetic-heavy and its CTAs are small (33 KB of shared memory, 256 threads): six of
 // them fill a dedicated SM; in the shared form they take whatever SMs the GEMM launches leave free
 int quant_grid(const PassCtx& x) {
-    if (x.comm_sms > 0) return x.dedicated ? x.comm_sms * 6 : std::max(4 * x.comm_sms, 2 * device_sm_count());
+    if (x.comm_sms > 0) return x.dedicated ? x.comm_sms * 6 : std::max(kThinCtasPerBudgetedSm * x.comm_sms, 2 * device_sm_count());
     return move_grid(x);
 }
 
