@@ -800,7 +800,7 @@ def run_ours(args, rank, world, local_rank):
         line["cuda_graph"] = {"ms_per_step": ms_graph, "value": flops / (ms_graph * 1e-3) / 1e12, "unit": UNIT,
                               "note": "the same step captured once with torch.cuda.graph and replayed"}
     # eight ranks: the MXFP8 half of the metric and the skewed-routing stress, each a short run of its own
-    if extras and world == 8 and name == "C3":
+    if (extras and world == 8 and name == "C3") or (args.sub_records and world > 1):
         F.clear_workspace_cache()
         torch.cuda.empty_cache()
         for key, sub, n_steps in (("mxfp8", "C4", 20), ("skew", "C5", 8)):
@@ -828,11 +828,24 @@ def run_ours(args, rank, world, local_rank):
         raise SystemExit("parity check failed: " + "; ".join(failed))
 
 
+def use_all_host_threads():
+    """The CPU arms use every hardware thread this process may run on.  (A launcher that starts one rank per GPU
+    exports OMP_NUM_THREADS=1 to each of them, which would leave the CPU baseline on a single thread.)"""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    if n > torch.get_num_threads():
+        torch.set_num_threads(n)
+    return torch.get_num_threads()
+
+
 def cpu_baseline(name, steps=1, warmup=0, sample_tokens=None, budget_s=None):
     """The CPU oracle on a bounded sample of the workload: same H, I, E, K and router law, fewer
     tokens per rank, single process, all host threads.  With `budget_s` the loop stops early once that much
     wall time is spent (the record says how many steps ran)."""
     from oracle import mok_oracle as O
+    use_all_host_threads()
     wl = WORKLOADS[name]
     W = 1
     T = sample_tokens or (min(wl["T"], 16384) if not wl["backward"] else 4096)   # about 3-10 s of CPU work per step
@@ -864,6 +877,7 @@ def cpu_c1(repeats=10):
     """The small CPU configuration: fp32 forward + backward of the layer (T=256, H=512, 8 experts, top-2, I=1024,
     seed 0) through the CPU oracle without the device's rounding points; median of `repeats` runs."""
     from oracle import mok_oracle as O
+    use_all_host_threads()
     wl = WORKLOADS["C1"]
     inp = [O.make_rank_inputs(0, T=wl["T"], H=wl["H"], I=wl["I"], E=wl["E"], W=1, K=wl["K"], seed=0)]
     O.layer_forward_backward(inp, device_rounding=False)
@@ -1029,6 +1043,8 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="skip the sampled-token parity check after the timed regions")
     ap.add_argument("--no-extras", action="store_true",
                     help="skip the single-GPU share of the workload and, at eight ranks, the MXFP8 and skew sub-records")
+    ap.add_argument("--sub-records", action="store_true",
+                    help="add the MXFP8 and skew sub-records at any rank count above one (they are automatic at eight)")
     ap.add_argument("--comm-sms", type=int, default=-1,
                     help="fwd/bwd_num_comm_sms of the MoKConfig (default: the configuration's own defaults)")
     ap.add_argument("--sweep-comm-sms", default="", help="comma-separated num_comm_sms values to time after the main run")

@@ -211,9 +211,10 @@ RowMoveParams row_move(const mok_layer_common& c, const PassCtx& x, const Dims& 
 // Shared form (default): the movers are thin bulk-copy CTAs, sixteen per budgeted SM, that sit beside the persistent
 // GEMM CTAs (24 KB of shared memory and three warps fit next to one) and fill an SM whenever no GEMM CTA holds it, so
 // the GEMMs keep every SM and the budget sets how many copy pipelines exist (the reference's defaults, 40 and 28 SMs,
-// give 640 and 448 mover CTAs; measured on two B200s the step gets shorter up to about 600 and flat beyond).  Dedicated form (MOK_B200_DEDICATED_COMM_SMS=1): that many SMs run fat mover
-// CTAs of their own and the routed GEMM grids shrink by the same number, as in the reference's megakernel.  Measured
-// on two B200s the shared form is 6 % faster, which is why it is the default.
+// give 640 and 448 mover CTAs; measured on two B200s the step gets shorter up to about 600 CTAs and stays flat beyond).
+// Dedicated form (MOK_B200_DEDICATED_COMM_SMS=1): that many SMs run fat mover CTAs of their own and the routed GEMM
+// grids shrink by the same number, as in the reference's megakernel.  Measured on two B200s the shared form is 5-6 %
+// faster than the best dedicated split, which is why it is the default.
 // With MOK_B200_OVERLAP_SHARED=1 even an unchunked window puts its load on the side stream, so that it runs beside
 // whatever the caller's stream holds since the last fork (the dense shared expert).  Off by default: measured on one
 // B200 the two kernels slow each other down by what the overlap saves (step within 1 % either way).
@@ -238,7 +239,7 @@ int env_int(const char* name, int fallback) {
 // MOK_B200_COMM_SMS: -1 / unset = take the budget from the call's num_comm_sms; 0 = no budget (four thin mover CTAs
 // per SM of the GPU whatever the call says); n > 0 = n SMs whatever the call says
 int comm_sm_override() {
-    static const int configured = [] { const int v = env_int("MOK_B200_COMM_SMS", -1); return v > 64 ? 64 : v; }();
+    static const int configured = env_int("MOK_B200_COMM_SMS", -1);
     return configured;
 }
 bool dedicated_comm_sms() {
@@ -385,13 +386,13 @@ int pipeline_chunks(const mok_layer_common& c, int limit) {
     return std::max(1, std::min(want, by_minibatch));
 }
 
-// SMs set aside for the row movers of this call: the caller's num_comm_sms when rows cross NVLink and the
-// window is processed in chunks, unless the environment overrides it; never more than half of the GPU
+// SM budget of the row movers of this call: the caller's num_comm_sms when rows cross NVLink and the window is
+// processed in chunks, unless the environment overrides it; dedicated SMs are capped at half of the GPU
 int pipeline_comm_sms(const mok_layer_common& c, int chunks) {
     if (chunks <= 1) return 0;
     const int forced = comm_sm_override();
     int n = forced >= 0 ? forced : (c.ep_size > 1 ? c.num_comm_sms : 0);
-    n = std::max(0, std::min(n, device_sm_count() / 2));
+    n = std::max(0, std::min(n, dedicated_comm_sms() ? device_sm_count() / 2 : device_sm_count()));
     return n & ~1;
 }
 

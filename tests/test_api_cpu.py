@@ -2,6 +2,7 @@
 exception classes raised before any launch, FakeTensor shape propagation, mutation schemas
 (reference: mok/functional.py:22-48, mok/ops.py validation blocks, tests/test_misc.py:582-1043)."""
 import dataclasses
+import os
 
 import pytest
 import torch
@@ -224,3 +225,23 @@ def test_bench_sampled_check_is_pinned_to_the_oracle():
             assert set(got) == {"output", "d_x", "d_router_weights"}
             for name, err in got.items():
                 assert err < 3e-3, (mx, rank, name, err)
+
+
+def test_bench_reference_arm_runs_on_rank_zero_only_and_c1_line(tmp_path):
+    """Launched as one rank per GPU, the reference arm is a single CPU process: every rank but 0 exits 0 without
+    work or output.  The small CPU configuration prints its own line (GFLOP/s, core count, median of >= 10)."""
+    import json
+    import subprocess
+    import sys
+    from tests.conftest import ROOT
+    bench_py = os.path.join(ROOT, "bench.py")
+    env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
+    idle = subprocess.run([sys.executable, bench_py, "--impl", "reference", "--gpus", "2", "--steps", "3", "--warmup", "1"],
+                          env=env, capture_output=True, text=True, timeout=300)
+    assert idle.returncode == 0 and idle.stdout.strip() == ""
+    c1 = subprocess.run([sys.executable, bench_py, "--workload", "C1", "--steps", "10"], capture_output=True, text=True,
+                        timeout=300)
+    assert c1.returncode == 0, c1.stderr[-2000:]
+    line = json.loads(c1.stdout.strip().splitlines()[-1])
+    assert line["impl"] == "reference" and line["unit"] == "GFLOP/s" and line["steps"] >= 10
+    assert line["cpu_baseline"]["cores"] >= 1 and line["value"] > 0
