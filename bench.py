@@ -620,6 +620,8 @@ def roofline_record(name, wl, res, steps, world):
                 burst_peak=burst, sustained_peak=sustained,
                 peak_source=peaks["source"] + (" bf16 figures x2 for fp8" if scale == 2.0 else ""),
                 traffic=dominant_traffic(name, E // world, res.get("n_rows")),
+                traffic_scope="one step: the launches_per_step launches of this kernel together cover the step's rows "
+                              "once and read each local expert's weights once; achieved is over the same launches",
                 launches_per_step=dom_cnt / steps if dom_cnt else 0, ms_per_step=dom_ms_step)
 
 
