@@ -364,13 +364,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                 if (p.row_scale) { const float w = p.row_scale[row]; inv_w = w > 0.0f ? 1.0f / w : 0.0f; }
                 float partial = 0.0f;
                 constexpr int kPer = kBlockN / 32 / kEpiSplit;
-                // the saved gate / up values of the next 32 columns are in flight while this chunk is computed
-                uint32_t gn[2][8], un[2][8];
-#pragma unroll
-                for (int v = 0; v < 2; ++v) {
-                    ld_global_256(p.in0 + off + (half * kPer) * 32 + v * 16, gn[v]);
-                    ld_global_256(p.in1 + off + (half * kPer) * 32 + v * 16, un[v]);
-                }
 #pragma unroll 1
                 for (int c = half * kPer; c < (half + 1) * kPer; ++c) {
                     uint32_t acc[32];
@@ -378,15 +371,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_const
                     uint32_t gv[2][8], uv[2][8];             // saved gate / up: two 256-bit loads each
 #pragma unroll
                     for (int v = 0; v < 2; ++v) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) { gv[v][i] = gn[v][i]; uv[v][i] = un[v][i]; }
-                    }
-                    if (c + 1 < (half + 1) * kPer) {
-#pragma unroll
-                        for (int v = 0; v < 2; ++v) {
-                            ld_global_256(p.in0 + off + (c + 1) * 32 + v * 16, gn[v]);
-                            ld_global_256(p.in1 + off + (c + 1) * 32 + v * 16, un[v]);
-                        }
+                        ld_global_256(p.in0 + off + c * 32 + v * 16, gv[v]);
+                        ld_global_256(p.in1 + off + c * 32 + v * 16, uv[v]);
                     }
                     tmem_ld_wait();
                     __nv_bfloat16* dh = p.out0 + off + c * 32;
