@@ -284,7 +284,7 @@ def sampled_parity(wl, rank, world, dev, inp, out, grads, sched, ctx, samples):
     block-quantised operands): output and, with a backward pass, d_x and d_router_weights — every routed row of
     those tokens was computed on the rank that owns its expert, so with several ranks this checks dispatch and
     combine end to end — plus eight rows of one routed expert's down-projection weight gradient (BF16 workloads),
-    contracted over the rows that expert received from all ranks.  Every rank's seeded inputs are regenerated
+    contracted over the rows that expert received from all ranks (their hidden activations recomputed here too).  Every rank's seeded inputs are regenerated
     here; nothing is read from another rank.  Returns {name: rel-L2}."""
     T, H, I, E, K = wl["T"], wl["H"], wl["I"], wl["E"], wl["K"]
     El = E // world
@@ -302,6 +302,7 @@ def sampled_parity(wl, rank, world, dev, inp, out, grads, sched, ctx, samples):
     pt0 = sched.peer_token_idx[:n_rows0].long()
     h_rows = torch.arange(0, H, H // 8, device=dev)[:8]
     d_y_rows = torch.zeros(n_rows0, len(h_rows), device=dev)
+    x_rows0 = torch.zeros(n_rows0, H, device=dev) if (wl["backward"] and not mx) else None   # what expert 0 received
     for p in range(world):
         step_p, params_p = make_inputs(wl, p, world, dev, pinned=False)
         for e in needed:
@@ -309,10 +310,13 @@ def sampled_parity(wl, rank, world, dev, inp, out, grads, sched, ctx, samples):
                 weights[e] = tuple(w[e - p * El].clone() for w in params_p[3:])
         if p == rank:
             shared = [w.float() for w in params_p[:3]]
-        if wl["backward"] and not mx and n_rows0 and ctx is not None:
+        if wl["backward"] and not mx and n_rows0:
             sel = pr0 == p
             tok, kk = pt0[sel] // K, pt0[sel] % K
             d_y_rows[sel] = rd(step_p["d_out"][tok][:, h_rows].float() * step_p["rw"][tok, kk][:, None])
+            x_rows0[sel] = step_p["x"][tok].float()
+            if p == rank:
+                w0 = tuple(w[0].float() for w in params_p[3:])       # this rank's first local expert
         del step_p, params_p
     x = inp["x"][idx].float()
     rw = inp["rw"][idx]
@@ -345,8 +349,11 @@ def sampled_parity(wl, rank, world, dev, inp, out, grads, sched, ctx, samples):
     if wl["backward"]:
         res["d_x"] = _rel_l2(rd(d_x), grads[0][idx].float())
         res["d_router_weights"] = _rel_l2(d_rw, grads[1][idx])
-        if not mx and n_rows0 and ctx is not None:
-            ref_rows = d_y_rows.T @ ctx.hidden_routed[:n_rows0].float()        # [8, I]
+        if not mx and n_rows0:
+            # hidden of the rows the first local expert received, recomputed from the senders' tokens (the saved
+            # activations are not used: a backward over several windows overwrites them with its replay)
+            hid0 = rd(_silu_fwd(rd(x_rows0 @ w0[0].T), rd(x_rows0 @ w0[1].T), None))
+            ref_rows = d_y_rows.T @ hid0                                       # [8, I]
             res["d_w_routed_down_rows"] = _rel_l2(ref_rows, grads[4][0][h_rows].float())
     return res
 

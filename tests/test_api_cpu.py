@@ -220,9 +220,10 @@ def test_bench_sampled_check_is_pinned_to_the_oracle():
             sched = types.SimpleNamespace(tokens_per_expert=torch.from_numpy(r["tokens_per_expert"]),
                                           peer_rank=torch.from_numpy(r["peer_rank"]),
                                           peer_token_idx=torch.from_numpy(r["peer_token_idx"]))
-            grads = (r["d_x"], r["d_router_weights"])
+            grads = tuple(r[n] for n in ("d_x", "d_router_weights", "d_w_routed_gate", "d_w_routed_up", "d_w_routed_down"))
             got = bench.sampled_parity(wl, rank, W, cpu, raw[rank][0], r["output"], grads, sched, None, 16)
-            assert set(got) == {"output", "d_x", "d_router_weights"}
+            want = {"output", "d_x", "d_router_weights"} | (set() if mx else {"d_w_routed_down_rows"})
+            assert set(got) == want
             for name, err in got.items():
                 assert err < 3e-3, (mx, rank, name, err)
 
