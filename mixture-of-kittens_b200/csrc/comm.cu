@@ -310,14 +310,16 @@ __global__ void __launch_bounds__(kMoveMaxWarps * 32, 8) move_rows_kernel(RowMov
 }
 
 // dispatch + MXFP8 quantisation.  Work unit = 32 consecutive rows (one MX block along the token axis)
-// x 256 columns.  Warp 0 fetches the 32 row pieces (512 B each, from whichever peer owns the row) with
-// cp.async.bulk into one of two shared-memory tiles while all eight warps quantise the other tile: one
-// 1x32 block along the row and one 32x1 block along the tokens per thread.  Padding rows are zeros
+// x kCols columns.  Warp 0 fetches the 32 row pieces (from whichever peer owns the row) with
+// cp.async.bulk into one of two shared-memory tiles while all warps quantise the other tile: 1x32
+// blocks along the rows and 32x1 blocks along the tokens.  Padding rows are zeros
 // (scale byte 88, as the reference's device code produces for an all-zero block).  kScale multiplies
 // every row by its route's router weight and re-rounds to bf16 first (backward "reverse combine").
-template <bool kScale>
-__global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, QuantOut o) {
-    constexpr int kCols = 256, kRowBytes = kCols * 2;
+// Two shapes: 256 threads on 32 x 256 tiles (33 KB; one block of each kind per thread), and a lean one of 64 threads
+// on 32 x 128 tiles (17 KB, at most 64 registers per thread) that fits in what an MXFP8 GEMM CTA leaves of an SM.
+template <bool kScale, int kThreads, int kCols>
+__global__ void __launch_bounds__(kThreads, 1024 / kThreads) dispatch_quant_kernel(RowMoveParams p, QuantOut o) {
+    constexpr int kRowBytes = kCols * 2, kRowBlocks = kCols / 32;
     __shared__ __align__(128) uint8_t tiles[2][32 * kRowBytes];
     __shared__ float s_w[2][32];
     __shared__ __align__(8) uint64_t bars[2];
@@ -371,8 +373,9 @@ __global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, Qu
         const int rb = unit / col_chunks, cc = unit - rb * col_chunks;
         const int row0 = row_lo + rb * 32, col0 = cc * kCols;
         const __nv_bfloat16* tile = reinterpret_cast<const __nv_bfloat16*>(tiles[buf]);
-        {   // normal: thread -> (row, 32-wide block)
-            const int r = threadIdx.x >> 3, kb = threadIdx.x & 7;
+#pragma unroll 1
+        for (int b = threadIdx.x; b < 32 * kRowBlocks; b += kThreads) {   // normal: (row, 32-wide block)
+            const int r = b / kRowBlocks, kb = b - r * kRowBlocks;
             uint32_t in[16], out[8], sb;
             const uint4* src = reinterpret_cast<const uint4*>(&tile[r * kCols + kb * 32]);
             const float w = s_w[buf][r];
@@ -387,8 +390,8 @@ __global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, Qu
                           out[5], out[6], out[7]);
             o.sc[mx_scale_offset(row0 + r, (col0 >> 5) + kb, p.hidden >> 7)] = static_cast<uint8_t>(sb);
         }
-        {   // transposed: thread -> column, block = the 32 rows
-            const int c = threadIdx.x;
+#pragma unroll 1
+        for (int c = threadIdx.x; c < kCols; c += kThreads) {   // transposed: a column, block = the 32 rows
             uint32_t in[16], out[8], sb;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
@@ -408,8 +411,13 @@ __global__ void __launch_bounds__(256) dispatch_quant_kernel(RowMoveParams p, Qu
 
 int launch_dispatch_quant(const RowMoveParams& p, const QuantOut& out, bool scale, int num_blocks, cudaStream_t stream) {
     ProfScope prof(kSlotDispatch, stream);
-    if (scale) dispatch_quant_kernel<true><<<num_blocks, 256, 0, stream>>>(p, out);
-    else dispatch_quant_kernel<false><<<num_blocks, 256, 0, stream>>>(p, out);
+    if (p.lean) {
+        if (scale) dispatch_quant_kernel<true, 64, 128><<<num_blocks, 64, 0, stream>>>(p, out);
+        else dispatch_quant_kernel<false, 64, 128><<<num_blocks, 64, 0, stream>>>(p, out);
+    } else {
+        if (scale) dispatch_quant_kernel<true, 256, 256><<<num_blocks, 256, 0, stream>>>(p, out);
+        else dispatch_quant_kernel<false, 256, 256><<<num_blocks, 256, 0, stream>>>(p, out);
+    }
     MOK_CUDA_CHECK(cudaGetLastError());
     return MOK_OK;
 }
